@@ -93,15 +93,32 @@ __device__ __forceinline__ float dot_head<bf16>(const float* __restrict__ q_shar
     return dot;
 }
 
+// What is added to a score beside the scaled product: `slope` > 0 takes slope * (position - j) off the
+// score of key j; `table` (or null) holds one learned number a distance, `stride` floats apart, and
+// table[min(position - j, rows - 1) * stride] is added (all distances from rows - 1 on share the last).
+struct ScoreBias {
+    float slope;
+    const float* table;
+    int rows;
+    int stride;
+};
+
+// The first key a query at `position` sees: the start of its window and of its own segment of
+// `segment` positions (segments are counted from position 0), whichever is later.
+__device__ __forceinline__ int first_visible(int position, int window, int segment) {
+    int lo = window > 0 ? max(0, position - window + 1) : 0;
+    if (segment > 0) lo = max(lo, position - position % segment);
+    return lo;
+}
+
 // One chunk of keys [first, last] (inclusive, inside one ATTN_CHUNK block) for one row.
-// `slope` > 0 takes slope * (position - j) off the score of key j; `value_stride`: elements from one
-// slot's value to the next (values may be a part of the key rows).
+// `value_stride`: elements from one slot's value to the next (values may be a part of the key rows).
 template <typename T, int DIMS>
 __device__ __forceinline__ void attend_chunk(
     Partial<DIMS>& part, const float* __restrict__ q_shared, const T* __restrict__ key_cache,
     const T* __restrict__ value_cache, const int* __restrict__ table, int first, int last,
     int kv_head, int num_kv, int head_dim, int value_dim, int64_t value_stride, int page_size, float scale,
-    float slope, int position, int lane) {
+    const ScoreBias& bias, int position, int lane) {
     part.max = -INFINITY;
     part.sum = 0.0f;
 #pragma unroll
@@ -115,7 +132,8 @@ __device__ __forceinline__ void attend_chunk(
             slot = ((int64_t)table[j / page_size] * num_kv + kv_head) * page_size + j % page_size;
             const T* k = key_cache + slot * head_dim;
             score = __fmul_rn(dot_head<T>(q_shared, k, head_dim), scale);
-            if (slope != 0.0f) score = __fsub_rn(score, __fmul_rn(slope, (float)(position - j)));
+            if (bias.slope != 0.0f) score = __fsub_rn(score, __fmul_rn(bias.slope, (float)(position - j)));
+            if (bias.table) score = __fadd_rn(score, bias.table[(int64_t)min(position - j, bias.rows - 1) * bias.stride]);
         }
         const float tile_max = warp_max(score);          // at least one key of a tile is valid
         const float new_max = fmaxf(part.max, tile_max);
@@ -147,22 +165,22 @@ __device__ __forceinline__ void attend_visible(
     Partial<DIMS>& part, const float* __restrict__ q_shared, const T* __restrict__ key_cache,
     const T* __restrict__ value_cache, const int* __restrict__ table, int chunk, int lo, int kept, int position,
     int kv_head, int num_kv, int head_dim, int value_dim, int64_t value_stride, int page_size, float scale,
-    float slope, int lane) {
+    const ScoreBias& bias, int lane) {
     const int begin = chunk * ATTN_CHUNK, end = begin + ATTN_CHUNK - 1;
     const int first = max(lo, begin), last = min(position, end);
     if (kept > begin) {                                   // kept = min(keep_first, lo): keys 0..kept-1
         attend_chunk<T, DIMS>(part, q_shared, key_cache, value_cache, table, begin, min(kept - 1, end), kv_head,
-                              num_kv, head_dim, value_dim, value_stride, page_size, scale, slope, position, lane);
+                              num_kv, head_dim, value_dim, value_stride, page_size, scale, bias, position, lane);
         if (first <= last) {
             Partial<DIMS> more;
             attend_chunk<T, DIMS>(more, q_shared, key_cache, value_cache, table, first, last, kv_head, num_kv,
-                                  head_dim, value_dim, value_stride, page_size, scale, slope, position, lane);
+                                  head_dim, value_dim, value_stride, page_size, scale, bias, position, lane);
             merge_partial(part, more);
         }
         return;
     }
     attend_chunk<T, DIMS>(part, q_shared, key_cache, value_cache, table, first, last, kv_head, num_kv, head_dim,
-                          value_dim, value_stride, page_size, scale, slope, position, lane);
+                          value_dim, value_stride, page_size, scale, bias, position, lane);
 }
 
 // Whether the query sees anything of a chunk.
@@ -182,6 +200,9 @@ struct RowExtras {
     const float* sinks;
     int gate_per_head;
     int64_t value_stride;
+    const float* bias_table;      // float32 [bias_rows, num_q] (or null): a learned number a distance and head
+    int bias_rows;
+    int segment;                  // > 0: a query sees only the keys of its own segment of so many positions
 };
 
 // (M, L, O) of a finished row -> output: the sink joins the denominator, then division, gate, rounding.
@@ -235,7 +256,7 @@ __global__ void paged_attention_rows_kernel(
             for (int i = lane; i < value_dim; i += 32) out_row[i] = from_float<T>(0.0f);
         return;
     }
-    const int lo = window > 0 ? max(0, position - window + 1) : 0;
+    const int lo = first_visible(position, window, extras.segment);
     const int kept = min(keep_first, lo);
     const int last_chunk = position / ATTN_CHUNK;
     if (SPLIT && !chunk_visible(blockIdx.y, lo, kept, position)) return;
@@ -244,13 +265,14 @@ __global__ void paged_attention_rows_kernel(
     __syncwarp();
     const int* table = block_tables + (int64_t)request * table_stride;
     const int kv_head = head / (num_q / num_kv);
-    const float slope = extras.slopes ? extras.slopes[head] : 0.0f;
+    const ScoreBias bias{extras.slopes ? extras.slopes[head] : 0.0f,
+                         extras.bias_table ? extras.bias_table + head : nullptr, extras.bias_rows, num_q};
 
     if (SPLIT) {
         const int chunk = blockIdx.y;
         Partial<DIMS> part;
         attend_visible<T, DIMS>(part, q_shared[warp], key_cache, value_cache, table, chunk, lo, kept, position,
-                                kv_head, num_kv, head_dim, value_dim, extras.value_stride, page_size, scale, slope,
+                                kv_head, num_kv, head_dim, value_dim, extras.value_stride, page_size, scale, bias,
                                 lane);
         float* dst = scratch + (row * max_chunks + chunk) * (int64_t)(value_dim + 2);
         if (lane == 0) { dst[0] = part.max; dst[1] = part.sum; }
@@ -270,7 +292,7 @@ __global__ void paged_attention_rows_kernel(
             Partial<DIMS> part;
             attend_visible<T, DIMS>(part, q_shared[warp], key_cache, value_cache, table, chunk, lo, kept, position,
                                     kv_head, num_kv, head_dim, value_dim, extras.value_stride, page_size, scale,
-                                    slope, lane);
+                                    bias, lane);
             merge_partial(total, part);
         }
         finish_row<T, DIMS>(total, extras.sinks, head, gate, gate_token_stride, extras.gate_per_head, token,
@@ -291,7 +313,7 @@ __global__ void merge_attention_rows_kernel(const float* __restrict__ scratch, i
     const int token = (int)(row / num_q), head = (int)(row % num_q);
     const int position = positions[token];
     if (token_row[token] < 0 || position < 0) return;     // zeros were written by the first kernel
-    const int lo = window > 0 ? max(0, position - window + 1) : 0;
+    const int lo = first_visible(position, window, extras.segment);
     const int kept = min(keep_first, lo);
     T* out_row = out + (int64_t)token * out_token_stride + (int64_t)head * head_dim;
     Partial<DIMS> total;
@@ -366,15 +388,19 @@ static void launch_rows(const void* q, long long q_token_stride, const void* key
 // of its own, one number a value or (`gate_per_head`) one a head, a distance bias (`slopes`), a sink in
 // the denominator (`sinks`), and values that lie `value_stride` elements apart (0: value_dim), which
 // lets them be a part of the key rows.
-extern "C" int tvb_attention_rows_biased(const void* q, long long q_token_stride, const void* key_cache,
+// `bias_table` (float32 [bias_rows, num_q], or null): table[min(p - j, bias_rows - 1), h] is added to the
+// score of key j; `segment` > 0: the query at p sees only keys from p - p % segment on.
+extern "C" int tvb_attention_rows_masked(const void* q, long long q_token_stride, const void* key_cache,
                                          const void* value_cache, long long value_stride, const int* block_tables,
                                          int table_stride, const int* token_row, const int* positions, void* out,
                                          long long out_token_stride, const void* gate, long long gate_token_stride,
                                          int gate_per_head, const float* slopes, const float* sinks,
+                                         const float* bias_table, int bias_rows, int segment,
                                          float* scratch, int max_chunks, int tokens, int num_q, int num_kv,
                                          int head_dim, int value_dim, int page_size, int window, int keep_first,
                                          float scale, int dtype, void* stream) {
     if (tokens <= 0) return 0;
+    if (segment < 0 || (bias_table && bias_rows <= 0)) return TVB_BAD_ARGUMENT;
     if (head_dim <= 0 || head_dim > 32 * ATTN_WIDE_DIMS || value_dim <= 0 || value_dim > 32 * ATTN_WIDE_DIMS ||
         num_q <= 0 || num_kv <= 0 || keep_first < 0 || value_stride < 0 ||
         num_q % num_kv || page_size <= 0 || max_chunks < 0 || max_chunks > 65535 ||
@@ -384,7 +410,8 @@ extern "C" int tvb_attention_rows_biased(const void* q, long long q_token_stride
     const int64_t blocks = (rows + ATTN_WARPS - 1) / ATTN_WARPS;
     if (blocks > 2147483647LL) return TVB_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    RowExtras extras{slopes, sinks, gate_per_head, value_stride > 0 ? value_stride : value_dim};
+    RowExtras extras{slopes, sinks, gate_per_head, value_stride > 0 ? value_stride : value_dim,
+                     bias_table, bias_rows, segment};
     const bool wide = head_dim > 32 * ATTN_MAX_DIMS || value_dim > 32 * ATTN_MAX_DIMS;
 #define LAUNCH_ROWS(T, DIMS)                                                                             \
     launch_rows<T, DIMS>(q, q_token_stride, key_cache, value_cache, block_tables, table_stride, token_row, \
@@ -396,6 +423,21 @@ extern "C" int tvb_attention_rows_biased(const void* q, long long q_token_stride
     else return TVB_BAD_ARGUMENT;
 #undef LAUNCH_ROWS
     return tvb_last_error();
+}
+
+extern "C" int tvb_attention_rows_biased(const void* q, long long q_token_stride, const void* key_cache,
+                                         const void* value_cache, long long value_stride, const int* block_tables,
+                                         int table_stride, const int* token_row, const int* positions, void* out,
+                                         long long out_token_stride, const void* gate, long long gate_token_stride,
+                                         int gate_per_head, const float* slopes, const float* sinks,
+                                         float* scratch, int max_chunks, int tokens, int num_q, int num_kv,
+                                         int head_dim, int value_dim, int page_size, int window, int keep_first,
+                                         float scale, int dtype, void* stream) {
+    return tvb_attention_rows_masked(q, q_token_stride, key_cache, value_cache, value_stride, block_tables,
+                                     table_stride, token_row, positions, out, out_token_stride, gate,
+                                     gate_token_stride, gate_per_head, slopes, sinks, nullptr, 0, 0, scratch,
+                                     max_chunks, tokens, num_q, num_kv, head_dim, value_dim, page_size, window,
+                                     keep_first, scale, dtype, stream);
 }
 
 extern "C" int tvb_attention_rows_general(const void* q, long long q_token_stride, const void* key_cache,

@@ -7,6 +7,10 @@
 //   v heads   [optional blend (1 - l) v + l v_first with a scalar l read from the device]
 //             -> written to the value cache
 //
+// With biases (float32: one number a column of the q heads, the k heads and the v heads) the projection
+// is taken as proj + bias, before anything else.  The v heads may be read from the k columns
+// (v_at == k_at): k is never changed where it stands.
+//
 // Keys are `key_dim` wide, values `value_dim`; the caches are [pages, num_kv, page, dim].
 // Rotation: the first `rot_dims` dimensions of a head turn by position * inv_freq[i]; pair i is
 // (2i, 2i + 1) with the interleaved pairing and (i, i + rot_dims / 2) with the half-split one;
@@ -59,7 +63,8 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) qkv_prepare_kernel(
     int value_dim, int norm_mode, const W* __restrict__ q_weight, const W* __restrict__ k_weight, float eps,
     const float* __restrict__ inv_freq, int rot_dims, int pairing, const int* __restrict__ positions,
     const int* __restrict__ slots, T* __restrict__ key_cache, T* __restrict__ value_cache, int page_size,
-    const T* v_first, int64_t v_first_stride, const T* __restrict__ blend, int tokens) {
+    const T* v_first, int64_t v_first_stride, const T* __restrict__ blend, int tokens,
+    const float* __restrict__ q_bias, const float* __restrict__ k_bias, const float* __restrict__ v_bias) {
     __shared__ float cos_s[32 * PAIRS], sin_s[32 * PAIRS];
     const int token = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -81,7 +86,10 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) qkv_prepare_kernel(
             const int g = head - num_q - num_kv;
             const T* src = token_row + v_at + (int64_t)g * value_dim;
             T* dst = value_cache + (((int64_t)(slot / page_size) * num_kv + g) * page_size + slot % page_size) * value_dim;
-            if (v_first) {
+            const float* vb = v_bias ? v_bias + (int64_t)g * value_dim : nullptr;
+            if (vb && !v_first) {
+                for (int i = lane; i < value_dim; i += 32) dst[i] = from_float<T>(__fadd_rn(to_float<T>(src[i]), vb[i]));
+            } else if (v_first) {
                 const float l = to_float<T>(blend[0]);
                 const float keep = __fsub_rn(1.0f, l);
                 const T* first = v_first + (int64_t)token * v_first_stride + (int64_t)g * value_dim;
@@ -114,6 +122,8 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) qkv_prepare_kernel(
                                        slot % page_size) * key_dim
                         : src;
         const W* weight = norm_mode == PREP_NORM_WEIGHT ? (is_key ? k_weight : q_weight) : nullptr;
+        const float* added = is_key ? (k_bias ? k_bias + (int64_t)(head - num_q) * key_dim : nullptr)
+                                    : (q_bias ? q_bias + (int64_t)head * key_dim : nullptr);
 
         // pair j of the head: the two dimensions it holds
         int at_a[PAIRS], at_b[PAIRS];
@@ -133,12 +143,14 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) qkv_prepare_kernel(
                     at_a[i] = 2 * j; at_b[i] = 2 * j + 1;
                     load_pair<T>(src + 2 * j, a[i], b[i]);
                 }
+                if (added) { a[i] = __fadd_rn(a[i], added[at_a[i]]); b[i] = __fadd_rn(b[i], added[at_b[i]]); }
                 squares = __fadd_rn(squares, __fmaf_rn(a[i], a[i], __fmul_rn(b[i], b[i])));
             }
         }
         // a head of an odd size has one value without a partner (never turned): lane 0 carries it
         const bool lone_here = (key_dim & 1) && lane == 0;
         float lone = lone_here ? to_float<T>(src[key_dim - 1]) : 0.0f;
+        if (lone_here && added) lone = __fadd_rn(lone, added[key_dim - 1]);
         squares = __fmaf_rn(lone, lone, squares);
         if (norm_mode != PREP_NORM_NONE) {
             squares = warp_sum(squares);
@@ -186,7 +198,8 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) qkv_prepare_wide_kernel(
     int value_dim, int norm_mode, const W* __restrict__ q_weight, const W* __restrict__ k_weight, float eps,
     const float* __restrict__ inv_freq, int rot_dims, const int* __restrict__ positions,
     const int* __restrict__ slots, bf16* __restrict__ key_cache, bf16* __restrict__ value_cache, int page_size,
-    const bf16* v_first, int64_t v_first_stride, const bf16* __restrict__ blend) {
+    const bf16* v_first, int64_t v_first_stride, const bf16* __restrict__ blend,
+    const float* __restrict__ q_bias, const float* __restrict__ k_bias, const float* __restrict__ v_bias) {
     __shared__ float cos_s[32 * PREP_MAX_PAIRS], sin_s[32 * PREP_MAX_PAIRS];
     const int token = blockIdx.x, tid = threadIdx.x;
     const int lanes = key_dim >> 3;                        // lanes a head: 2, 4, 8, 16 or 32
@@ -206,8 +219,15 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) qkv_prepare_wide_kernel(
         const bool is_key = head >= num_q;
         bf16* src = token_row + (is_key ? k_at + (int64_t)(head - num_q) * key_dim : q_at + (int64_t)head * key_dim) + c * 8;
         float x[8];
-        if (live) unpack_bf16x8(ld_global_16(src), x);
-        else {
+        if (live) {
+            unpack_bf16x8(ld_global_16(src), x);
+            const float* added = is_key ? (k_bias ? k_bias + (int64_t)(head - num_q) * key_dim + c * 8 : nullptr)
+                                        : (q_bias ? q_bias + (int64_t)head * key_dim + c * 8 : nullptr);
+            if (added) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[i] = __fadd_rn(x[i], added[i]);
+            }
+        } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) x[i] = 0.0f;
         }
@@ -245,6 +265,13 @@ __global__ void __launch_bounds__(PREP_WARPS * 32) qkv_prepare_wide_kernel(
     for (int item = tid; item < num_kv * per_head; item += blockDim.x) {
         const int g = item / per_head, c = item % per_head;
         uint4 word = ld_global_16(token_row + v_at + (int64_t)g * value_dim + c * 8);
+        if (v_bias) {
+            float x[8];
+            unpack_bf16x8(word, x);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = __fadd_rn(x[i], v_bias[(int64_t)g * value_dim + c * 8 + i]);
+            word = pack_bf16x8(x);
+        }
         if (v_first) {
             float x[8], f[8];
             unpack_bf16x8(word, x);
@@ -262,14 +289,15 @@ static int launch_prepare(void* proj, long long token_stride, int q_at, int k_at
                           int key_dim, int value_dim, int norm_mode, const void* qw, const void* kw, float eps,
                           const float* inv_freq, int rot_dims, int pairing, const int* positions, const int* slots,
                           void* key_cache, void* value_cache, int page_size, const void* v_first,
-                          long long v_first_stride, const void* blend, int tokens, cudaStream_t s) {
+                          long long v_first_stride, const void* blend, int tokens, const float* q_bias,
+                          const float* k_bias, const float* v_bias, cudaStream_t s) {
     const int heads = num_q + 2 * num_kv;
     const dim3 grid((unsigned)tokens, (unsigned)((heads + PREP_WARPS - 1) / PREP_WARPS));
 #define GO(PAIRS)                                                                                                   \
     qkv_prepare_kernel<T, W, PAIRS><<<grid, PREP_WARPS * 32, 0, s>>>(                                               \
         (T*)proj, token_stride, q_at, k_at, v_at, num_q, num_kv, key_dim, value_dim, norm_mode, (const W*)qw,       \
         (const W*)kw, eps, inv_freq, rot_dims, pairing, positions, slots, (T*)key_cache, (T*)value_cache,           \
-        page_size, (const T*)v_first, v_first_stride, (const T*)blend, tokens)
+        page_size, (const T*)v_first, v_first_stride, (const T*)blend, tokens, q_bias, k_bias, v_bias)
     if (key_dim <= 64) GO(1);
     else if (key_dim <= 128) GO(2);
     else GO(PREP_MAX_PAIRS);
@@ -277,13 +305,15 @@ static int launch_prepare(void* proj, long long token_stride, int q_at, int k_at
     return tvb_last_error();
 }
 
-extern "C" int tvb_qkv_prepare(void* proj, long long token_stride, int q_at, int k_at, int v_at, int num_q,
+extern "C" int tvb_qkv_prepare_biased(void* proj, long long token_stride, int q_at, int k_at, int v_at, int num_q,
                                int num_kv, int key_dim, int value_dim, int norm_mode, const void* q_weight,
                                const void* k_weight, int weight_dtype, float eps, const float* inv_freq,
                                int rot_dims, int pairing, const int* positions, const int* slots,
                                void* key_cache, void* value_cache, int page_size, const void* v_first,
-                               long long v_first_stride, const void* blend, int tokens, int dtype, void* stream) {
+                               long long v_first_stride, const void* blend, int tokens, int dtype,
+                               const float* q_bias, const float* k_bias, const float* v_bias, void* stream) {
     if (tokens <= 0) return 0;
+    if (v_bias && v_first) return TVB_BAD_ARGUMENT;          // a blended value has no bias of its own here
     if (key_dim <= 0 || key_dim > 64 * PREP_MAX_PAIRS || value_dim <= 0 || num_q <= 0 || num_kv < 0 ||
         num_q + 2 * num_kv > 65535 * PREP_WARPS || (slots && page_size <= 0) || norm_mode < 0 || norm_mode > 2 ||
         (norm_mode == PREP_NORM_WEIGHT && (!q_weight || !k_weight)) ||
@@ -302,17 +332,29 @@ extern "C" int tvb_qkv_prepare(void* proj, long long token_stride, int q_at, int
     qkv_prepare_wide_kernel<W><<<(unsigned)tokens, PREP_WARPS * 32, 0, s>>>(                                        \
         (bf16*)proj, token_stride, q_at, k_at, v_at, num_q, num_kv, key_dim, value_dim, norm_mode,                  \
         (const W*)q_weight, (const W*)k_weight, eps, inv_freq, rot_dims, positions, slots, (bf16*)key_cache,        \
-        (bf16*)value_cache, page_size, (const bf16*)v_first, v_first_stride, (const bf16*)blend)
+        (bf16*)value_cache, page_size, (const bf16*)v_first, v_first_stride, (const bf16*)blend, q_bias, k_bias, v_bias)
         if (weight_dtype == TVB_F32) WIDE(float); else WIDE(bf16);
 #undef WIDE
         return tvb_last_error();
     }
 #define GO(T, W) return launch_prepare<T, W>(proj, token_stride, q_at, k_at, v_at, num_q, num_kv, key_dim, value_dim, \
         norm_mode, q_weight, k_weight, eps, inv_freq, rot_dims, pairing, positions, slots, key_cache, value_cache,    \
-        page_size, v_first, v_first_stride, blend, tokens, s)
+        page_size, v_first, v_first_stride, blend, tokens, q_bias, k_bias, v_bias, s)
     if (dtype == TVB_F32 && weight_dtype == TVB_F32) GO(float, float);
     if (dtype == TVB_BF16 && weight_dtype == TVB_BF16) GO(bf16, bf16);
     if (dtype == TVB_BF16 && weight_dtype == TVB_F32) GO(bf16, float);
 #undef GO
     return TVB_BAD_ARGUMENT;
+}
+
+extern "C" int tvb_qkv_prepare(void* proj, long long token_stride, int q_at, int k_at, int v_at, int num_q,
+                               int num_kv, int key_dim, int value_dim, int norm_mode, const void* q_weight,
+                               const void* k_weight, int weight_dtype, float eps, const float* inv_freq,
+                               int rot_dims, int pairing, const int* positions, const int* slots,
+                               void* key_cache, void* value_cache, int page_size, const void* v_first,
+                               long long v_first_stride, const void* blend, int tokens, int dtype, void* stream) {
+    return tvb_qkv_prepare_biased(proj, token_stride, q_at, k_at, v_at, num_q, num_kv, key_dim, value_dim, norm_mode,
+                                  q_weight, k_weight, weight_dtype, eps, inv_freq, rot_dims, pairing, positions, slots,
+                                  key_cache, value_cache, page_size, v_first, v_first_stride, blend, tokens, dtype,
+                                  nullptr, nullptr, nullptr, stream);
 }

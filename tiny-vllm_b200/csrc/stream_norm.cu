@@ -71,6 +71,7 @@ extern "C" int tvb_stream_norm(const float* stream_in, const void* add1, const v
     cudaStream_t s = (cudaStream_t)stream;
 #define GO(A, T, W) return launch_stream_norm<A, T, W>(stream_in, add1, add2, weight, y, stream_out, gather, rows, width, eps, pdl, s)
     if (dtype == TVB_F32 && weight_dtype == TVB_F32 && add_dtype == TVB_F32) GO(float, float, float);
+    if (dtype == TVB_F32 && weight_dtype == TVB_F32 && add_dtype == TVB_BF16) GO(bf16, float, float);   // a normed embedding
     if (dtype == TVB_BF16 && weight_dtype == TVB_BF16 && add_dtype == TVB_F32) GO(float, bf16, bf16);
     if (dtype == TVB_BF16 && weight_dtype == TVB_BF16 && add_dtype == TVB_BF16) GO(bf16, bf16, bf16);
     if (dtype == TVB_BF16 && weight_dtype == TVB_F32 && add_dtype == TVB_F32) GO(float, bf16, float);

@@ -23,19 +23,20 @@ from .model import Model
 from .step import StepEntry, StepRunner
 
 PAGE_SIZE = 16
-MAX_LIVE_REQUESTS = 16
+MAX_LIVE_REQUESTS = 4
 
 
 def build_runner(model_dir, dtype: str, max_tokens: int, *, page_size: int = PAGE_SIZE,
-                 device: str = "cuda:0") -> StepRunner:
-    """Model of ``model_dir`` with a page pool for ``max_tokens`` tokens in every group."""
+                 max_requests: int = MAX_LIVE_REQUESTS, device: str = "cuda:0") -> StepRunner:
+    """Model of ``model_dir`` with a page pool for ``max_tokens`` tokens in every group and state slots
+    for ``max_requests`` live requests."""
     torch_dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype]
     if not torch.cuda.is_available():
         raise RuntimeError("trace replay runs the CUDA kernels and needs a GPU; none is visible")
     config = read_model_config(model_dir)
     model = Model(config.to_spec(), device=device, dtype=torch_dtype).load(model_dir)
     pages = -(-max_tokens // page_size)
-    return StepRunner(model, page_size=page_size, num_pages=pages, max_requests=MAX_LIVE_REQUESTS,
+    return StepRunner(model, page_size=page_size, num_pages=pages, max_requests=max_requests,
                       max_model_len=pages * page_size)
 
 
@@ -75,11 +76,14 @@ def main(argv=None) -> int:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at any time (each rounded up to 64)")
     parser.add_argument("--page-size", type=int, default=PAGE_SIZE)
+    parser.add_argument("--max-requests", type=int, default=MAX_LIVE_REQUESTS,
+                        help="state slots: the most requests that are live at any time")
     args = parser.parse_args(argv)
-    if args.max_tokens <= 0 or args.page_size <= 0:
-        parser.error("--max-tokens and --page-size must be positive")
+    if args.max_tokens <= 0 or args.page_size <= 0 or args.max_requests <= 0:
+        parser.error("--max-tokens, --page-size and --max-requests must be positive")
     print(f"[trace_run] loading {args.model} ({args.dtype})", file=sys.stderr, flush=True)
-    runner = build_runner(args.model, args.dtype, args.max_tokens, page_size=args.page_size)
+    runner = build_runner(args.model, args.dtype, args.max_tokens, page_size=args.page_size,
+                          max_requests=args.max_requests)
     torch.backends.cuda.matmul.allow_tf32 = False
     with torch.inference_mode():
         replay(runner, sys.stdin, Path(args.out),

@@ -270,9 +270,17 @@ def windowed_attention(ctx, mixer, projected: torch.Tensor, at: int, run: int, o
     group = ctx.storage.group_of(run)
     writes = ctx.writes_cache(run)
     q_at, k_at = at, at + mixer.q_cols
-    v_at = k_at + mixer.k_cols
-    g_at = v_at + mixer.v_cols
-    v_here = projected[:, v_at:v_at + mixer.v_cols]
+    values_are_keys = getattr(mixer, "values_are_keys", False)
+    # values that are the keys as projected are read from the keys' columns, which nothing changes in place
+    v_at = k_at if values_are_keys else k_at + mixer.k_cols
+    g_at = k_at + mixer.k_cols + mixer.v_cols
+    v_here = projected[:, v_at:v_at + mixer.num_kv_heads * mixer.value_dim]
+    q_bias, k_bias = getattr(mixer, "q_bias", None), getattr(mixer, "k_bias", None)
+    bias_table, segment = getattr(mixer, "bias_table", None), getattr(mixer, "segment", None)
+    if values_are_keys and not writes:
+        raise kernels.KernelError("values that are the keys need the step's keys written to the cache")
+    if mixer.qk_norm == "whole" and (q_bias is not None or values_are_keys):
+        raise kernels.KernelError("biases and values that are keys go with a norm a head, not with the whole norm")
     v_first = None
     if mixer.value_mix == "first":
         ctx.shared[mixer.value_mix_key] = v_here
@@ -308,13 +316,14 @@ def windowed_attention(ctx, mixer, projected: torch.Tensor, at: int, run: int, o
             rot_dims=0 if position is None else position.rot_dims,
             pairing="interleaved" if position is None else position.pairing,
             slots=ctx.slots[group] if writes else None, key_cache=keys, value_cache=values,
-            v_first=v_first, blend=mixer.vmix if v_first is not None else None)
+            v_first=v_first, blend=mixer.vmix if v_first is not None else None,
+            q_bias=q_bias, k_bias=k_bias, v_bias=k_bias if values_are_keys else None)
     gate = projected[:, g_at:g_at + mixer.gate_cols] if mixer.gate else None
     queries = projected[:, q_at:q_at + mixer.q_cols]
     heads = dict(num_q=mixer.num_heads, num_kv=mixer.num_kv_heads, key_dim=mixer.key_dim,
                  value_dim=mixer.value_dim, window=mixer.window, keep_first=mixer.keep_first, scale=mixer.scale,
                  gate_per_head=mixer.gate == "head", slopes=mixer.slopes, sinks=mixer.sinks)
-    if windowed_on_tensor_cores(mixer, projected, q_at, g_at, out):
+    if bias_table is None and segment is None and windowed_on_tensor_cores(mixer, projected, q_at, g_at, out):
         # bfloat16: prompt portions in tiles of 64 tokens, single tokens (decoded ones, whose keys are in the
         # cache by now) one CTA per kv head and chunk of keys
         def singles(part):
@@ -345,7 +354,7 @@ def windowed_attention(ctx, mixer, projected: torch.Tensor, at: int, run: int, o
         ctx.token_row, ctx.positions, num_q=mixer.num_heads, num_kv=mixer.num_kv_heads, head_dim=mixer.key_dim,
         value_dim=mixer.value_dim, window=mixer.window, keep_first=mixer.keep_first, scale=mixer.scale,
         gate=gate, gate_per_head=mixer.gate == "head", slopes=mixer.slopes, sinks=mixer.sinks, out=out,
-        scratch=scratch, max_chunks=ctx.split_chunks)
+        scratch=scratch, max_chunks=ctx.split_chunks, bias_table=bias_table, segment=segment)
 
 
 def latent_attention(ctx, mixer, projected: torch.Tensor, run: int) -> torch.Tensor:

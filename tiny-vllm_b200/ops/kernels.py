@@ -302,7 +302,8 @@ def attention_rows(q: torch.Tensor, q_token_stride: int, key_cache: torch.Tensor
                    value_dim: int | None = None, keep_first: int = 0,
                    gate: torch.Tensor | None = None, gate_per_head: bool = False,
                    slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None,
-                   value_offset: int | None = None) -> torch.Tensor:
+                   value_offset: int | None = None, bias_table: torch.Tensor | None = None,
+                   segment: int | None = None) -> torch.Tensor:
     """Paged causal attention, one warp per (token, head).
 
     ``q`` holds the query heads of token t at ``t * q_token_stride`` elements
@@ -315,8 +316,17 @@ def attention_rows(q: torch.Tensor, q_token_stride: int, key_cache: torch.Tensor
     one number a head; ``out`` may have strided rows too.  ``slopes`` (float32 [num_q]): slope *
     (position - j) is taken off the score of key j; ``sinks`` (float32 [num_q]): exp(sink) joins the
     softmax's denominator once.  ``value_offset``: the values are the ``value_dim`` elements from
-    there on of every key row (``value_cache`` is then None)."""
-    _need_cuda(q, key_cache, value_cache, block_tables, token_row, positions, scratch, gate, slopes, sinks)
+    there on of every key row (``value_cache`` is then None).  ``bias_table`` (float32 [rows, num_q]):
+    table[min(position - j, rows - 1), head] is added to the score of key j; ``segment``: the query at
+    position p sees only the keys from p - p % segment on."""
+    _need_cuda(q, key_cache, value_cache, block_tables, token_row, positions, scratch, gate, slopes, sinks,
+               bias_table)
+    if bias_table is not None and (bias_table.dtype != torch.float32 or bias_table.dim() != 2
+                                   or bias_table.shape[1] != num_q or bias_table.shape[0] < 1
+                                   or not bias_table.is_contiguous()):
+        raise KernelError("attention_rows: the bias table must be contiguous float32 [distances, num_q]")
+    if segment is not None and segment <= 0:
+        raise KernelError("attention_rows: a segment holds at least one position")
     tokens = positions.shape[0]
     value_dim = head_dim if value_dim is None else value_dim
     if head_dim > ATTENTION_ROWS_MAX_DIM or value_dim > ATTENTION_ROWS_MAX_DIM or num_q % num_kv:
@@ -354,14 +364,15 @@ def attention_rows(q: torch.Tensor, q_token_stride: int, key_cache: torch.Tensor
         need = attention_rows_scratch_floats(tokens, num_q, value_dim, max_chunks)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
             raise KernelError(f"attention_rows: split mode needs {need} float32 of scratch")
-    fn = _fn("attention_rows", "tvb_attention_rows_biased",
+    fn = _fn("attention_rows", "tvb_attention_rows_masked",
              [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-              c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-              c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+              c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
     _check(fn(q.data_ptr(), q_token_stride, key_cache.data_ptr(), value_ptr, value_stride,
               block_tables.data_ptr(), block_tables.shape[1], token_row.data_ptr(),
               positions.data_ptr(), out.data_ptr(), out.stride(0), _ptr(gate),
               0 if gate is None else gate.stride(0), 1 if gate_per_head else 0, _ptr(slopes), _ptr(sinks),
+              _ptr(bias_table), 0 if bias_table is None else bias_table.shape[0], segment or 0,
               _ptr(scratch), max_chunks, tokens, num_q, num_kv,
               head_dim, value_dim, key_cache.shape[2], window or 0, keep_first if window else 0, scale,
               dtype_tag(q.dtype), _stream()),
@@ -688,6 +699,130 @@ def route_act(logits: torch.Tensor, up: torch.Tensor, *, experts: int, top: int,
               dtype_tag(up.dtype), _stream()), "route_act")
     return out
 
+def route_gated_act(logits: torch.Tensor, proj: torch.Tensor, *, experts: int, top: int, ff: int, shared_ff: int,
+                    limit: float, shared_limit: float, alpha: float, route_scale: float = 1.0,
+                    correction: torch.Tensor | None = None, groups: int = 1, keep: int = 1,
+                    shared_gated: bool = False, out: torch.Tensor | None = None,
+                    weights_out: torch.Tensor | None = None) -> torch.Tensor:
+    """Sigmoid routing and gated experts with limits between the packed input and output products.
+
+    ``logits`` float32 [tokens, experts (+ 1 with ``shared_gated``: the shared expert's gate logit)];
+    ``proj`` [tokens, 2 * (experts * ff + shared_ff)] holds [gate | up] of every expert, then of the shared
+    one.  Scores are sigmoid(logits); the ``top`` experts with the largest score + ``correction`` among
+    the ``keep`` best of ``groups`` groups (a group's score: the sum of its two largest) are chosen and
+    weighted score / (sum of the chosen scores + 1e-20) * ``route_scale``.  The result [tokens, experts * ff
+    + shared_ff] holds min(gate, limit) * sigmoid(alpha * that) * (clamp(up, -limit, limit) + 1) times the
+    expert's weight (0 if not chosen); the shared expert's columns use ``shared_limit`` and the weight
+    sigmoid(its gate logit), or 1."""
+    _need_cuda(logits, proj, correction, out, weights_out)
+    tokens = proj.shape[0]
+    columns = experts * ff + shared_ff
+    if logits.dtype != torch.float32 or logits.shape != (tokens, experts + (1 if shared_gated else 0)) \
+            or logits.stride(1) != 1:
+        raise KernelError("route_gated_act: router logits are float32 [tokens, experts (+ 1)]")
+    if proj.dim() != 2 or proj.shape[1] != 2 * columns or proj.stride(1) != 1 \
+            or not 0 < experts <= ROUTE_MAX_EXPERTS or top <= 0:
+        raise KernelError("route_gated_act: the projection must be [tokens, 2 * (experts * ff + shared_ff)]")
+    if groups <= 0 or experts % groups or not 0 < keep <= groups:
+        raise KernelError("route_gated_act: experts form equal groups of which some are kept")
+    if correction is not None and (correction.dtype != torch.float32 or correction.shape != (experts,)
+                                   or not correction.is_contiguous()):
+        raise KernelError("route_gated_act: the correction is contiguous float32 [experts]")
+    if out is None:
+        out = torch.empty((tokens, columns), dtype=proj.dtype, device=proj.device)
+    elif out.shape != (tokens, columns) or out.dtype != proj.dtype or out.stride(1) != 1:
+        raise KernelError("route_gated_act: out must be [tokens, experts * ff + shared_ff] of the projection's dtype")
+    if weights_out is not None and (weights_out.dtype != torch.float32 or weights_out.shape != (tokens, experts)
+                                    or not weights_out.is_contiguous()):
+        raise KernelError("route_gated_act: weights_out must be contiguous float32 [tokens, experts]")
+    fn = _fn("routed_act", "tvb_route_gated_act",
+             [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_int,
+              c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_float, c_float, c_float, c_int, c_void_p])
+    _check(fn(logits.data_ptr(), logits.stride(0), _ptr(correction), proj.data_ptr(), proj.stride(0),
+              out.data_ptr(), out.stride(0), _ptr(weights_out), tokens, experts, top, groups, keep, route_scale,
+              ff, shared_ff, 1 if shared_gated else 0, limit, shared_limit, alpha, dtype_tag(proj.dtype),
+              _stream()), "route_gated_act")
+    return out
+
+
+# --------------------------------------------------- retention: linear attention with a decay a head
+RETENTION_MAX_DIM = 256
+RETENTION_ACTS = {None: 0, "silu": 1, "sigmoid": 2}
+
+
+def retention(proj: torch.Tensor, *, q_at: int, k_at: int, v_at: int, g_at: int | None, heads: int, dim: int,
+              vdim: int, decay: torch.Tensor, state: torch.Tensor, row_starts: torch.Tensor,
+              state_slots: torch.Tensor, token_row: torch.Tensor, positions: torch.Tensor,
+              inv_freq: torch.Tensor | None = None, rot_dims: int = 0, pairing: str = "half_split",
+              key_scale: float = 1.0, unit_norm: bool = True, eps: float = 0.0, gate_act: str | None = "silu",
+              out: torch.Tensor | None = None, raw_out: torch.Tensor | None = None) -> torch.Tensor:
+    """Retention between a mixer's packed input projection and its output projection.
+
+    ``proj`` [tokens, columns] holds q heads (``dim`` wide) from column ``q_at``, k heads from ``k_at``,
+    v heads (``vdim``) from ``v_at`` and, with ``g_at``, a gate of heads * vdim columns.  Per request
+    (``row_starts`` [rows + 1] first flat token of every entry, ``state_slots`` [rows]) and head, token by
+    token: S <- decay_h S + k v^T, o = S^T q, from the float32 ``state`` [slots, heads, dim, vdim] of the
+    request's slot, which is left as the state after the step's last token.  q and k are turned by
+    position * ``inv_freq`` on their first ``rot_dims`` dimensions and k is multiplied by ``key_scale``,
+    all in float32.  Every head's o is divided by its root mean square (``unit_norm``, with ``eps``),
+    multiplied by act(gate) and rounded to the projection's type: [tokens, heads * vdim].  ``raw_out``
+    (float32 [tokens, heads * vdim]) receives o itself."""
+    _need_cuda(proj, decay, state, row_starts, state_slots, token_row, positions, inv_freq, out, raw_out)
+    tokens = proj.shape[0]
+    rows = state_slots.shape[0]
+    if proj.dim() != 2 or proj.stride(1) != 1:
+        raise KernelError("retention: the projection must be [tokens, columns] with contiguous rows")
+    ends = [q_at + heads * dim, k_at + heads * dim, v_at + heads * vdim] + ([] if g_at is None else [g_at + heads * vdim])
+    if min(q_at, k_at, v_at, 0 if g_at is None else g_at) < 0 or max(ends) > proj.shape[1]:
+        raise KernelError("retention: the heads do not fit the projection's rows")
+    if not 0 < dim <= RETENTION_MAX_DIM or vdim <= 0:
+        raise KernelError(f"retention takes key sizes up to {RETENTION_MAX_DIM}, not {dim}")
+    if state.dtype != torch.float32 or state.dim() != 4 or state.shape[1:] != (heads, dim, vdim) \
+            or not state.is_contiguous():
+        raise KernelError("retention: the state is contiguous float32 [slots, heads, dim, vdim]")
+    if decay.dtype != torch.float32 or decay.shape != (heads,) or not decay.is_contiguous():
+        raise KernelError("retention: decay is contiguous float32 [heads]")
+    for name, t, shape in (("row_starts", row_starts, (rows + 1,)), ("state_slots", state_slots, (rows,)),
+                           ("token_row", token_row, (tokens,)), ("positions", positions, (tokens,))):
+        if t.dtype != torch.int32 or t.shape != shape or not t.is_contiguous():
+            raise KernelError(f"retention: {name} must be contiguous int32 {list(shape)}")
+    if inv_freq is not None and (inv_freq.dtype != torch.float32 or inv_freq.shape != (rot_dims // 2,) or rot_dims % 2
+                                 or not 0 < rot_dims <= dim or not inv_freq.is_contiguous()):
+        raise KernelError("retention: inv_freq must be float32 [rot_dims / 2] with rot_dims <= dim")
+    if pairing not in PAIRINGS or gate_act not in RETENTION_ACTS:
+        raise KernelError(f"retention: pairing {pairing!r} or gate activation {gate_act!r} is not known")
+    if out is None:
+        out = torch.empty((tokens, heads * vdim), dtype=proj.dtype, device=proj.device)
+    elif out.shape != (tokens, heads * vdim) or out.dtype != proj.dtype or out.stride(1) != 1:
+        raise KernelError("retention: out must be [tokens, heads * vdim] of the projection's dtype")
+    if raw_out is None:
+        raw_out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=proj.device)
+    elif raw_out.shape != (tokens, heads * vdim) or raw_out.dtype != torch.float32 or not raw_out.is_contiguous():
+        raise KernelError("retention: raw_out must be contiguous float32 [tokens, heads * vdim]")
+    turned = torch.empty((2, tokens, heads * dim), dtype=torch.float32, device=proj.device)
+    tag = dtype_tag(proj.dtype)
+    prepare = _fn("retention", "tvb_retention_prepare",
+                  [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p,
+                   c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(prepare(proj.data_ptr(), proj.stride(0), q_at, k_at, heads, dim, _ptr(inv_freq), rot_dims,
+                   PAIRINGS[pairing], key_scale, positions.data_ptr(), turned[0].data_ptr(), turned[1].data_ptr(),
+                   tokens, tag, _stream()), "retention_prepare")
+    scan = _fn("retention", "tvb_retention_scan",
+               [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(scan(turned[0].data_ptr(), turned[1].data_ptr(), proj.data_ptr() + v_at * proj.element_size(),
+                proj.stride(0), state.data_ptr(), decay.data_ptr(), row_starts.data_ptr(), state_slots.data_ptr(),
+                token_row.data_ptr(), raw_out.data_ptr(), rows, heads, dim, vdim, tag, _stream()), "retention_scan")
+    finish = _fn("retention", "tvb_retention_finish",
+                 [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_float, c_int,
+                  c_int, c_void_p])
+    gate_ptr = None if g_at is None else proj.data_ptr() + g_at * proj.element_size()
+    _check(finish(raw_out.data_ptr(), gate_ptr, proj.stride(0), out.data_ptr(), out.stride(0), tokens, heads, vdim,
+                  1 if unit_norm else 0, eps, RETENTION_ACTS[gate_act if g_at is not None else None], tag,
+                  _stream()), "retention_finish")
+    return out
+
+
 # ------------------- q/k norm, rotation, value blend and cache write with every size a parameter
 NORM_MODES = {None: 0, "unit": 1, "weight": 2}
 PAIRINGS = {"interleaved": 0, "half_split": 1}
@@ -698,15 +833,27 @@ def qkv_prepare(proj: torch.Tensor, *, q_at: int, k_at: int, v_at: int, num_q: i
                 q_weight: torch.Tensor | None = None, k_weight: torch.Tensor | None = None, eps: float = 0.0,
                 inv_freq: torch.Tensor | None = None, rot_dims: int = 0, pairing: str = "interleaved",
                 slots: torch.Tensor | None, key_cache: torch.Tensor | None, value_cache: torch.Tensor | None,
-                v_first: torch.Tensor | None = None, blend: torch.Tensor | None = None) -> None:
+                v_first: torch.Tensor | None = None, blend: torch.Tensor | None = None,
+                q_bias: torch.Tensor | None = None, k_bias: torch.Tensor | None = None,
+                v_bias: torch.Tensor | None = None) -> None:
     """In place on a packed projection [tokens, columns] that holds the q heads from column
     ``q_at``, the k heads from ``k_at`` and the v heads from ``v_at``: q and k heads are normalised
     over the head (``norm`` None, "unit" or "weight") and rotated (``inv_freq`` float32
     [rot_dims / 2]; the angle is position * inv_freq in float32), q where it stands, k into
     ``key_cache`` [pages, num_kv, page, key_dim] at ``slots``; v heads go to ``value_cache``
     [pages, num_kv, page, value_dim], blended as (1 - blend) v + blend v_first when ``v_first``
-    [tokens, num_kv * value_dim] (rows may be strided) and the one-element ``blend`` are given."""
-    _need_cuda(proj, positions, q_weight, k_weight, inv_freq, slots, key_cache, value_cache, v_first, blend)
+    [tokens, num_kv * value_dim] (rows may be strided) and the one-element ``blend`` are given.
+    ``q_bias`` [num_q * key_dim], ``k_bias`` [num_kv * key_dim], ``v_bias`` [num_kv * value_dim] (float32):
+    added to the projection's columns before anything else.  ``v_at`` may equal ``k_at``: the values are
+    then the keys as projected (k is not changed where it stands)."""
+    _need_cuda(proj, positions, q_weight, k_weight, inv_freq, slots, key_cache, value_cache, v_first, blend,
+               q_bias, k_bias, v_bias)
+    for name, t, size in (("q_bias", q_bias, num_q * key_dim), ("k_bias", k_bias, num_kv * key_dim),
+                          ("v_bias", v_bias, num_kv * value_dim)):
+        if t is not None and (t.dtype != torch.float32 or t.shape != (size,) or not t.is_contiguous()):
+            raise KernelError(f"qkv_prepare: {name} must be contiguous float32 [{size}]")
+    if v_bias is not None and v_first is not None:
+        raise KernelError("qkv_prepare: blended values take no bias")
     tokens = proj.shape[0]
     if proj.dim() != 2 or proj.stride(1) != 1:
         raise KernelError("qkv_prepare: the projection must be [tokens, columns] with contiguous rows")
@@ -741,16 +888,17 @@ def qkv_prepare(proj: torch.Tensor, *, q_at: int, k_at: int, v_at: int, num_q: i
                 or v_first.shape != (tokens, num_kv * value_dim) or v_first.stride(1) != 1):
             raise KernelError("qkv_prepare: v_first [tokens, num_kv * value_dim] and a one-element blend, both "
                               "of the projection's dtype")
-    fn = _fn("qkv_prepare", "tvb_qkv_prepare",
+    fn = _fn("qkv_prepare", "tvb_qkv_prepare_biased",
              [c_void_p, c_longlong] + [c_int] * 8 + [c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int,
                                                     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                                    c_longlong, c_void_p, c_int, c_int, c_void_p])
+                                                    c_longlong, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                                    c_void_p, c_void_p])
     _check(fn(proj.data_ptr(), proj.stride(0), q_at, k_at, v_at, num_q, num_kv, key_dim, value_dim,
               NORM_MODES[norm], _ptr(q_weight), _ptr(k_weight), weight_tag, eps, _ptr(inv_freq), rot_dims,
               PAIRINGS[pairing], positions.data_ptr(), _ptr(slots), _ptr(key_cache), _ptr(value_cache),
               key_cache.shape[2] if slots is not None else 0, _ptr(v_first),
               0 if v_first is None else v_first.stride(0), _ptr(blend), tokens, dtype_tag(proj.dtype),
-              _stream()), "qkv_prepare")
+              _ptr(q_bias), _ptr(k_bias), _ptr(v_bias), _stream()), "qkv_prepare")
 
 
 

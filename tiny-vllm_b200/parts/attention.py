@@ -92,6 +92,22 @@ class GQAAttention(Part):
         return linear_into_stream(attended, self.o_weight, residual)
 
 
+def distance_buckets(rows: int, far: float) -> list[int]:
+    """The bucket of every distance 0 .. ceil(far): n itself below rows / 2, then logarithmic steps that
+    reach the last bucket, rows - 1, at ``far``; evaluated in double precision."""
+    import math
+
+    half = rows // 2
+    buckets = []
+    for n in range(int(math.ceil(far)) + 1):
+        if n < half:
+            buckets.append(n)
+        else:
+            step = int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half)))
+            buckets.append(min(rows - 1, half + step))
+    return buckets
+
+
 class WindowedAttention(Part):
     """Grouped-query attention with every size and step a parameter.
 
@@ -114,6 +130,15 @@ class WindowedAttention(Part):
     the gate is one number a head, sigmoid(W_g x)_h with W_g [heads, width].  ``float32_output``: the
     output projection leaves its float32 sums unrounded (for a float32 residual sum).
 
+    ``qk_bias``: q and k have biases (tensors ``q_bias`` / ``k_bias``), added to the projection in float32
+    before anything else.  ``values_are_keys``: there is no value projection; a token's values are its
+    keys as projected (bias included), before their norm and rotation.  ``distance_table`` (rows, far):
+    a learned number a head and distance bucket (tensor ``rel`` [rows, heads]; a checkpoint's tensor
+    decides ``rows`` by its shape) is added to the scaled score; distance n < rows / 2 has the bucket n, a larger one min(rows - 1, rows / 2 + floor(ln(n /
+    (rows / 2)) / ln(far / (rows / 2)) * (rows - rows / 2))).  ``segment``: the positions form segments
+    of so many, counted from position 0, and a query sees only the keys of its own.  ``sink`` may also be
+    a number: a sink of that fixed score for every head.
+
     ``hosted=True``: a block computes the input projections of all its parts as one product and
     the output projections as another; the mixer then owns no matrices, names its share
     (``input_rows``, ``output_cols``) and works between the two products (``between``)."""
@@ -124,7 +149,9 @@ class WindowedAttention(Part):
                  position=None, gate: bool | str = False, value_mix: str | None = None,
                  value_mix_key: str = "v_first", names: dict | None = None, hosted: bool = False,
                  query_temperature: tuple | None = None, distance_slope_exponent: float | None = None,
-                 sink: bool = False, float32_output: bool = False) -> None:
+                 sink: bool | float = False, float32_output: bool = False, qk_bias: bool = False,
+                 values_are_keys: bool = False, distance_table: tuple | None = None,
+                 segment: int | None = None) -> None:
         if num_heads % num_kv_heads:
             raise ValueError("query heads must be a multiple of key-value heads")
         limit = kernels.ATTENTION_ROWS_MAX_DIM
@@ -142,6 +169,17 @@ class WindowedAttention(Part):
             raise ValueError("a window holds at least one key")
         if keep_first < 0:
             raise ValueError("keep_first must not be negative")
+        if values_are_keys and (value_dim != key_dim or value_mix is not None):
+            raise ValueError("values that are the keys have the keys' size and are not blended")
+        if segment is not None and segment <= 0:
+            raise ValueError("a segment holds at least one position")
+        if distance_table is not None:
+            rows, far = int(distance_table[0]), float(distance_table[1])
+            if rows < 2 or not far > rows // 2:
+                raise ValueError("a distance table has at least two rows and reaches beyond its linear half")
+            distance_table = (rows, far)
+        self.qk_bias, self.values_are_keys = bool(qk_bias), bool(values_are_keys)
+        self.distance_table, self.segment = distance_table, segment
         self.hidden_size = hidden_size
         self.num_heads, self.num_kv_heads = num_heads, num_kv_heads
         self.key_dim, self.value_dim = key_dim, value_dim
@@ -157,12 +195,14 @@ class WindowedAttention(Part):
         if self.query_temperature is not None and self.query_temperature[1] <= 0:
             raise ValueError("the query temperature's period must be positive")
         self.distance_slope_exponent = None if distance_slope_exponent is None else float(distance_slope_exponent)
-        self.has_sink = bool(sink)
+        self.has_sink = sink is True
+        self.fixed_sink = None if isinstance(sink, bool) else float(sink)
         self.out_dtype = torch.float32 if float32_output else None
         self.device = ctx.device
         self.slopes = self.sinks = self.sink = None
+        self.q_bias = self.k_bias = self.rel = self.bias_table = None
         n = {"q": "q", "k": "k", "v": "v", "g": "g", "o": "o", "vmix": "vmix", "q_norm": "q_norm",
-             "k_norm": "k_norm", "sink": "sink", **(names or {})}
+             "k_norm": "k_norm", "sink": "sink", "q_bias": "q.b", "k_bias": "k.b", "rel": "rel", **(names or {})}
         self.names = {key: f"{ctx.prefix}.{value}" for key, value in n.items()}
         self.position = ctx.build("position", position, ctx) if position is not None else None
         self.in_weight = self.o_weight = self.vmix = self.q_norm_weight = self.k_norm_weight = None
@@ -178,7 +218,8 @@ class WindowedAttention(Part):
 
     @property
     def v_cols(self) -> int:
-        return self.num_kv_heads * self.value_dim
+        """Columns of the value projection (none when the values are the keys)."""
+        return 0 if self.values_are_keys else self.num_kv_heads * self.value_dim
 
     @property
     def out_cols(self) -> int:
@@ -192,12 +233,15 @@ class WindowedAttention(Part):
     def plain(self) -> bool:
         """No distance bias, no sink, a gate (if any) of one number a value, keys and values apart:
         what the tensor-core kernels of the windowed attention take."""
-        return self.distance_slope_exponent is None and not self.has_sink and self.gate != "head"
+        return (self.distance_slope_exponent is None and not self.has_sink and self.fixed_sink is None
+                and self.gate != "head" and self.distance_table is None and self.segment is None)
 
     def input_rows(self):
         """(checkpoint tensor, rows) of the input projections, in the order of their columns:
         q heads, k heads, v heads and, with a gate, the gate."""
-        rows = [(self.names["q"], self.q_cols), (self.names["k"], self.k_cols), (self.names["v"], self.v_cols)]
+        rows = [(self.names["q"], self.q_cols), (self.names["k"], self.k_cols)]
+        if not self.values_are_keys:
+            rows.append((self.names["v"], self.v_cols))
         if self.gate:
             rows.append((self.names["g"], self.gate_cols))
         return rows
@@ -225,6 +269,13 @@ class WindowedAttention(Part):
                                        role="vector", init="around_one")]
         if self.has_sink:
             specs.append(ParamSpec.single("sink", self.names["sink"], (self.num_heads,), role="vector"))
+        if self.qk_bias:
+            specs += [ParamSpec.single("q_bias", self.names["q_bias"], (self.q_cols,), role="vector"),
+                      ParamSpec.single("k_bias", self.names["k_bias"], (self.k_cols,), role="vector")]
+        if self.distance_table is not None:
+            # the table's own shape says how many buckets there are; distance_table[0] only sizes random weights
+            specs.append(ParamSpec.single("rel", self.names["rel"], (self.distance_table[0], self.num_heads),
+                                          role="table", free_rows=True))
         return specs
 
     def finalize(self) -> None:
@@ -235,6 +286,19 @@ class WindowedAttention(Part):
                 torch.float32).to(self.device)
         if self.has_sink and self.sink is not None:
             self.sinks = self.sink.to(torch.float32).contiguous()
+        if self.fixed_sink is not None:
+            self.sinks = torch.full((self.num_heads,), self.fixed_sink, dtype=torch.float32, device=self.device)
+        if self.qk_bias and self.q_bias is not None:
+            self.q_bias = self.q_bias.to(torch.float32).contiguous()
+            self.k_bias = self.k_bias.to(torch.float32).contiguous()
+        if self.distance_table is not None and self.rel is not None:
+            # one row a distance: the kernels read table[min(distance, rows - 1)], and every distance from
+            # ``far`` on has the last bucket
+            if self.rel.shape[0] < 2 or not self.distance_table[1] > self.rel.shape[0] // 2:
+                raise ValueError("a distance table has at least two rows and reaches beyond its linear half")
+            buckets = distance_buckets(self.rel.shape[0], self.distance_table[1])
+            index = torch.tensor(buckets, dtype=torch.long, device=self.rel.device)
+            self.bias_table = self.rel.to(torch.float32).index_select(0, index).contiguous()
 
     def children(self):
         return [self.position] if self.position is not None else []

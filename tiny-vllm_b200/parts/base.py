@@ -83,11 +83,13 @@ class ParamSpec:
     role: str = "matrix"
     init: str = "normal"
     optional: bool = False        # a checkpoint may lack it: the part is then bound None (random weights draw none)
+    free_rows: bool = False       # the checkpoint decides the first dimension (one source); ``shape[0]`` is only
+                                  # what random weights are drawn with, and the part reads the size off the tensor
 
     @staticmethod
     def single(attr: str, name: str, shape: tuple[int, ...], *, role: str = "matrix",
-               init: str = "normal", optional: bool = False) -> "ParamSpec":
-        return ParamSpec(attr, shape, (ParamSource(name, 0, shape[0]),), role, init, optional)
+               init: str = "normal", optional: bool = False, free_rows: bool = False) -> "ParamSpec":
+        return ParamSpec(attr, shape, (ParamSource(name, 0, shape[0]),), role, init, optional, free_rows)
 
     @staticmethod
     def scalar(attr: str, name: str, *, init: str = "unit_interval") -> "ParamSpec":

@@ -16,15 +16,29 @@ from .registry import register_part
 
 
 class PreNormResidualBlock(Block):
+    """x <- x + mixer(norm1(x)), then x <- x + feed_forward(norm2(x)); a layer may have no feed-forward
+    (``feed_forward`` None: the layer ends after its mixer and declares no second norm).
+    ``bare_norm_names``: the norms' weights are stored as "<layer>.<norm name>" instead of
+    "<layer>.<norm name>.weight"."""
+
     def __init__(self, ctx: BuildContext, *, mixer, feed_forward, norm, mixer_norm_name: str,
-                 feed_forward_norm_name: str, mixer_name: str, feed_forward_name: str) -> None:
-        self.mixer_norm = ctx.build("norm", norm, ctx.child(mixer_norm_name))
+                 feed_forward_norm_name: str, mixer_name: str, feed_forward_name: str,
+                 bare_norm_names: bool = False) -> None:
+        def build_norm(name):
+            if bare_norm_names:
+                return ctx.build("norm", norm.with_params(name=f"{ctx.prefix}.{name}"), ctx)
+            return ctx.build("norm", norm, ctx.child(name))
+
+        self.mixer_norm = build_norm(mixer_norm_name)
         self.mixer = ctx.build("mixer", mixer, ctx.child(mixer_name))
-        self.feed_forward_norm = ctx.build("norm", norm, ctx.child(feed_forward_norm_name))
-        self.feed_forward = ctx.build("feed_forward", feed_forward, ctx.child(feed_forward_name))
+        self.feed_forward_norm = self.feed_forward = None
+        if feed_forward is not None:
+            self.feed_forward_norm = build_norm(feed_forward_norm_name)
+            self.feed_forward = ctx.build("feed_forward", feed_forward, ctx.child(feed_forward_name))
 
     def children(self):
-        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        return [part for part in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+                if part is not None]
 
     def forward(self, hidden, residual, ctx, run: int):
         # a part that can take its norm into its first projection does so (forward_normed
@@ -35,6 +49,8 @@ class PreNormResidualBlock(Block):
         else:
             x, residual = _normed(self.mixer_norm, hidden, residual)
             mixed = self.mixer.forward(x, ctx, run)
+        if self.feed_forward is None:
+            return mixed, residual
         if hasattr(self.feed_forward, "forward_normed"):
             return self.feed_forward.forward_normed(mixed, residual, self.feed_forward_norm, ctx)
         x, residual = _normed(self.feed_forward_norm, mixed, residual)

@@ -14,15 +14,25 @@ from .registry import register_part
 
 
 class TokenEmbedding(Part):
-    def __init__(self, ctx: BuildContext, *, vocab_size: int, width: int, name: str) -> None:
+    """h = E[ids]; with ``norm`` (a norm part that offers ``start``) the rows are normed at once and leave
+    in float32, as the first tensor of a float32 residual stream."""
+
+    def __init__(self, ctx: BuildContext, *, vocab_size: int, width: int, name: str, norm=None) -> None:
         self.vocab_size, self.width, self.name = vocab_size, width, name
         self.weight = None
+        self.norm = ctx.build("norm", norm, ctx) if norm is not None else None
+        if self.norm is not None and not hasattr(self.norm, "start"):
+            raise ValueError("an embedding's norm must offer start(x)")
 
     def param_specs(self):
         return [ParamSpec.single("weight", self.name, (self.vocab_size, self.width), role="table")]
 
+    def children(self):
+        return [self.norm] if self.norm is not None else []
+
     def forward(self, token_ids):
-        return kernels.embed_rows(self.weight, token_ids)
+        rows = kernels.embed_rows(self.weight, token_ids)
+        return rows if self.norm is None else self.norm.start(rows)
 
 
 class LMHead(Part):

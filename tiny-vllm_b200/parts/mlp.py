@@ -22,13 +22,16 @@ from .registry import register_part
 
 class SwiGLU(Part):
     def __init__(self, ctx: BuildContext, *, hidden_size: int, intermediate_size: int,
-                 names: dict | None = None, activation: str = "silu", hosted: bool = False) -> None:
+                 names: dict | None = None, activation: str = "silu", hosted: bool = False,
+                 float32_output: bool = False) -> None:
         if activation not in kernels.ACTIVATIONS:
             raise ValueError(f"activation is one of {', '.join(kernels.ACTIVATIONS)}, not {activation!r}")
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
         self.activation = activation
         self.hosted = hosted
+        # the down projection leaves its float32 sums unrounded (for a float32 residual sum)
+        self.out_dtype = torch.float32 if float32_output else None
         n = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight",
              **(names or {})}
         self.names = {key: f"{ctx.prefix}.{value}" for key, value in n.items()}
@@ -70,12 +73,12 @@ class SwiGLU(Part):
                                  self.intermediate_size, self.activation)
 
     def forward(self, x, ctx):
-        return linear(self._activated(x), self.down_weight)
+        return linear(self._activated(x), self.down_weight, out_dtype=self.out_dtype)
 
     def forward_normed(self, hidden, residual, norm, ctx):
         """forward(norm(hidden + residual)) and the new residual stream; the output is None when
         the down projection has added it to the stream itself."""
-        if self.activation != "silu":
+        if self.activation != "silu" or self.out_dtype is not None:
             if hidden is None:
                 x = norm.forward(residual)
             elif residual is None:
@@ -142,3 +145,77 @@ class RoutedExperts(Part):
 
 
 register_part("feed_forward", "routed_experts", RoutedExperts)
+
+
+class GatedRoutedExperts(Part):
+    """A mixture of gated experts with sigmoid routing, without biases.
+
+    An expert: g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), y = g * sigmoid(alpha * g) *
+    (u + 1), output W_down y.  Router logits z = W_router h are float32, the scores s = sigmoid(z).  A token
+    uses the ``top`` experts with the largest choice scores s + correction (tensor ``correction``, with
+    ``correction=True``); the experts form ``groups`` equal groups of neighbours, a group's score is the
+    sum of its two largest choice scores, and only experts of the ``keep`` best groups can be chosen.  The
+    chosen experts' weights are their scores s divided by their sum (+ 1e-20), times ``route_scale``.  A
+    shared expert of the same form (``shared_ff`` wide, 0 for none, with ``shared_limit``) runs for every
+    token and is added, multiplied by sigmoid(W_sg h), one number a token (``shared_gate``).
+
+    As in :class:`RoutedExperts` the experts are two products: [gate_e | up_e] of all experts and of the
+    shared one are the rows of one weight, the down-projections stand side by side in another, and one
+    kernel between the two routes, activates and weights (exactly 0 for experts not chosen).  The
+    router's rows and the shared expert's gate row are one small float32-result product."""
+
+    def __init__(self, ctx: BuildContext, *, hidden_size: int, experts: int, top: int, ff: int, limit: float,
+                 alpha: float, route_scale: float = 1.0, correction: bool = False, groups: int = 1, keep: int = 1,
+                 shared_ff: int = 0, shared_limit: float | None = None, shared_gate: bool = False,
+                 float32_output: bool = False, names: dict | None = None) -> None:
+        if not 0 < top <= experts or experts > kernels.ROUTE_MAX_EXPERTS:
+            raise ValueError(f"a token uses between 1 and all of at most {kernels.ROUTE_MAX_EXPERTS} experts")
+        if groups <= 0 or experts % groups or not 0 < keep <= groups:
+            raise ValueError("experts form equal groups of which at least one and at most all are kept")
+        if shared_gate and not shared_ff:
+            raise ValueError("a gate of the shared expert needs a shared expert")
+        self.hidden_size, self.experts, self.top, self.ff, self.shared_ff = hidden_size, experts, top, ff, shared_ff
+        self.limit, self.alpha, self.route_scale = float(limit), float(alpha), float(route_scale)
+        self.shared_limit = float(limit if shared_limit is None else shared_limit)
+        self.has_correction, self.groups, self.keep, self.shared_gate = bool(correction), groups, keep, bool(shared_gate)
+        self.out_dtype = torch.float32 if float32_output else None
+        n = {"router": "router", "correction": "correction", "expert": "e{index}", "shared": "shared",
+             "gate": "gate", "up": "up", "down": "down", "shared_gate": "sg", **(names or {})}
+        self.router_sources = [(f"{ctx.prefix}.{n['router']}", experts)]
+        if shared_gate:
+            self.router_sources.append((f"{ctx.prefix}.{n['shared']}.{n['shared_gate']}", 1))
+        self.correction_name = f"{ctx.prefix}.{n['correction']}"
+        stems = [f"{ctx.prefix}.{n['expert'].format(index=index)}" for index in range(experts)]
+        if shared_ff:
+            stems.append(f"{ctx.prefix}.{n['shared']}")
+        sizes = [ff] * experts + ([shared_ff] if shared_ff else [])
+        self.in_sources = [(f"{stem}.{n[which]}", size) for stem, size in zip(stems, sizes) for which in ("gate", "up")]
+        self.down_sources = [(f"{stem}.{n['down']}", size) for stem, size in zip(stems, sizes)]
+        self.router_weight = self.in_weight = self.down_weight = self.correction = None
+
+    def param_specs(self):
+        specs = [ParamSpec.packed("router_weight", self.router_sources, self.hidden_size),
+                 ParamSpec.packed("in_weight", self.in_sources, self.hidden_size),
+                 ParamSpec.side_by_side("down_weight", self.hidden_size, self.down_sources)]
+        if self.has_correction:
+            specs.append(ParamSpec.single("correction", self.correction_name, (self.experts,), role="vector"))
+        return specs
+
+    def finalize(self) -> None:
+        if self.correction is not None:
+            self.correction = self.correction.to(torch.float32).contiguous()
+
+    def streamed_weights(self):
+        return [self.in_weight, self.down_weight]
+
+    def forward(self, x, ctx):
+        logits = linear(x, self.router_weight, out_dtype=torch.float32)
+        inner = kernels.route_gated_act(
+            logits, linear(x, self.in_weight), experts=self.experts, top=self.top, ff=self.ff,
+            shared_ff=self.shared_ff, limit=self.limit, shared_limit=self.shared_limit, alpha=self.alpha,
+            route_scale=self.route_scale, correction=self.correction, groups=self.groups, keep=self.keep,
+            shared_gated=self.shared_gate)
+        return linear(inner, self.down_weight, out_dtype=self.out_dtype)
+
+
+register_part("feed_forward", "gated_routed_experts", GatedRoutedExperts)

@@ -46,15 +46,29 @@ class StreamRMSNorm(Part):
     storage type or float32) and keeps s, in place, as the new stream.  The stream is float32
     also where activations and weights are bfloat16."""
 
-    def __init__(self, ctx: BuildContext, *, width: int, eps: float, name: str | None = None) -> None:
+    def __init__(self, ctx: BuildContext, *, width: int, eps: float, name: str | None = None,
+                 unit_offset: bool = False) -> None:
         self.width = width
         self.eps = float(eps)
         self.name = name if name is not None else f"{ctx.prefix}.weight"
         self.out_dtype = ctx.dtype
+        self.unit_offset = bool(unit_offset)   # the checkpoint stores w around zero and the norm multiplies by 1 + w
         self.weight = None
 
     def param_specs(self):
-        return [ParamSpec.single("weight", self.name, (self.width,), role="vector", init="around_one")]
+        return [ParamSpec.single("weight", self.name, (self.width,), role="vector",
+                                 init="normal" if self.unit_offset else "around_one")]
+
+    def finalize(self) -> None:
+        if self.unit_offset and self.weight is not None and not getattr(self, "_offset_applied", False):
+            self.weight = (self.weight.to(torch.float32) + 1.0).contiguous()      # 1 + w, once, in float32
+            self._offset_applied = True
+
+    def start(self, x):
+        """norm(x) in float32: the first tensor of a float32 stream (a normed embedding)."""
+        if x.dtype == torch.float32:
+            return kernels.stream_norm(x, self.weight, self.eps, out_dtype=torch.float32, rows=None)[0]
+        return kernels.stream_norm(None, self.weight, self.eps, add=x, out_dtype=torch.float32)[0]
 
     def forward(self, x):
         """norm(x) for a float32 stream or for activations that start one."""

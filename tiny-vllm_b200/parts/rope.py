@@ -101,5 +101,13 @@ class RopeInterleaved(Part):
         self.inv_freq = self.inverse_frequencies().to(self.device)
 
 
+class RopeHalfSplitComputed(RopeInterleaved):
+    """The same encoding without tables, but with the halves paired: dimension i of the first ``dims``
+    dimensions of a head turns together with dimension i + dims / 2, by position * base^(-2i / dims)."""
+
+    pairing = "half_split"
+
+
 register_part("position", "rope_half_split", RopeHalfSplit)
 register_part("position", "rope_interleaved", RopeInterleaved)
+register_part("position", "rope_half_split_computed", RopeHalfSplitComputed)

@@ -118,10 +118,15 @@ def bind_tensors(targets, named_tensors, *, dtype, device, folder="<memory>",
             continue
         part, spec, source = route
         want = source_shape(spec, source)
+        key = (id(part), spec.attr)
+        if spec.free_rows and len(spec.sources) == 1 and tensor.dim() == len(want) and tensor.shape[0] > 0 \
+                and tuple(tensor.shape[1:]) == want[1:]:
+            # the tensor itself says how many rows it has
+            destinations[key] = tensor.to(device=device, dtype=storage_dtype_of(spec, tensor.dtype, dtype)).contiguous()
+            continue
         if tuple(tensor.shape) != want:
             wrong.append((name, want, tuple(tensor.shape)))
             continue
-        key = (id(part), spec.attr)
         if key not in destinations:
             destinations[key] = torch.empty(
                 spec.shape, dtype=storage_dtype_of(spec, tensor.dtype, dtype), device=device)
