@@ -68,6 +68,30 @@ def distance_bucket(n: int, rows: int, bias_max: int) -> int:
     return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(bias_max / half) * (rows - half))))
 
 
+def bias_matrix(rel, tokens, bias_max):
+    """[heads, tokens, tokens]: the table's entry for the distance i - j (0 where j > i)."""
+    by_distance = torch.tensor([distance_bucket(n, rel.shape[0], bias_max) for n in range(tokens)])
+    i = torch.arange(tokens)[:, None]
+    j = torch.arange(tokens)[None, :]
+    bucket = by_distance[(i - j).clamp(min=0)]
+    return rel[bucket].permute(2, 0, 1)
+
+
+def chunk_mask(tokens, size):
+    """[tokens, tokens], true where query i sees key j: j <= i, both in the same chunk of ``size``
+    positions counted from 0 (``size`` None: no chunks)."""
+    i = torch.arange(tokens)[:, None]
+    j = torch.arange(tokens)[None, :]
+    seen = j <= i
+    return seen if size is None else seen & (i // size == j // size)
+
+
+def softmax_with_one_more(scores, seen):
+    """exp(s_j) / (1 + sum over the seen keys of exp(s_j)): one more term of score 0 that has no value."""
+    e = torch.where(seen, torch.exp(scores), torch.zeros_like(scores))
+    return e / (1.0 + e.sum(-1, keepdim=True))
+
+
 def chunked_attention(h, w, prefix, mixer, eps):
     """The attention mixer on a whole sequence ``h`` [tokens, width] that begins at position 0."""
     heads, groups, dim = mixer["heads"], mixer["kv_heads"], mixer["dim"]
@@ -77,20 +101,14 @@ def chunked_attention(h, w, prefix, mixer, eps):
     v = k                                                   # the values are the keys before their norm
     q = rms(q, eps) * w[prefix + ".q.norm"]
     k = rms(k, eps) * w[prefix + ".k.norm"]
-    rel = w[prefix + ".rel"]
-    size = mixer["mask"]["size"]
+    mask = mixer.get("mask")
+    seen = chunk_mask(tokens, None if mask is None else mask["size"])
+    bias = bias_matrix(w[prefix + ".rel"], tokens, mixer["bias_max"])
     out = torch.zeros(tokens, heads, mixer["vdim"], dtype=h.dtype)
     for head in range(heads):
         kv = head // (heads // groups)
-        for i in range(tokens):
-            first = i // size * size
-            js = list(range(first, i + 1))
-            scores = (k[js, kv] @ q[i, head]) * mixer["scale"]
-            scores = scores + torch.stack([rel[distance_bucket(i - j, rel.shape[0], mixer["bias_max"]), head]
-                                           for j in js])
-            e = torch.exp(scores)
-            p = e / (1.0 + e.sum())
-            out[i, head] = p @ v[js, kv]
+        scores = (q[:, head] @ k[:, kv].T) * mixer["scale"] + bias[head]
+        out[:, head] = softmax_with_one_more(scores, seen) @ v[:, kv]
     gate = torch.sigmoid(h @ w[prefix + ".g"].T)
     return (out.reshape(tokens, -1) * gate) @ w[prefix + ".o"].T
 
@@ -153,7 +171,10 @@ def forward(config, weights, tokens, dtype=torch.float64, layer_outputs=None):
     eps = config["norm"]["eps"]
     x = norm_one_plus(w["embed"][torch.as_tensor(tokens)], w["embed.norm"], eps)
     for index, layer in enumerate(config["layers"]):
-        p = f"l{layer.get('weights_of', index)}"
+        owner = index
+        while config["layers"][owner].get("weights_of") is not None:
+            owner = config["layers"][owner]["weights_of"]
+        p = f"l{owner}"
         h = norm_one_plus(x, w[p + ".norm1"], eps)
         if layer["type"] == "retention":
             x = x + retention(h, w, p + ".mix", layer["mixer"], eps)[0]
@@ -164,3 +185,11 @@ def forward(config, weights, tokens, dtype=torch.float64, layer_outputs=None):
         if layer_outputs is not None:
             layer_outputs.append(x.clone())
     return norm_one_plus(x, w["final.norm"], eps) @ w["head"].T
+
+
+def greedy(config, weights, prompt, new_tokens: int) -> list[int]:
+    """``new_tokens`` tokens after ``prompt``, each the largest logit of the whole sequence run again."""
+    tokens = list(prompt)
+    for _ in range(new_tokens):
+        tokens.append(int(forward(config, weights, tokens)[-1].argmax()))
+    return tokens[len(prompt):]

@@ -108,3 +108,18 @@ class CacheStorage:
         index = torch.as_tensor(list(slots), dtype=torch.long, device=self.device)
         for arena in self.state.values():
             arena.index_fill_(0, index, 0)
+
+    def snapshot_state(self, slots):
+        """Copies of the state rows of ``slots`` (None without state): what a step that is run a second
+        time, to settle a graph capture, has to start from again."""
+        if not self.state or not slots:
+            return None
+        index = torch.tensor(sorted(set(slots)), dtype=torch.long, device=next(iter(self.state.values())).device)
+        return index, {run: arena.index_select(0, index) for run, arena in self.state.items()}
+
+    def restore_state(self, snapshot) -> None:
+        if snapshot is None:
+            return
+        index, rows = snapshot
+        for run, saved in rows.items():
+            self.state[run].index_copy_(0, index, saved)

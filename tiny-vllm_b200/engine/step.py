@@ -389,16 +389,20 @@ class StepRunner:
             # the replay launched the kernels with bounded waits behind the back of their wrappers
             kernels.note_guarded_launches(*graph.guarded)
             return graph.logits
+        capturing = prepared.capture and self._step_graph_limit > 0
+        # recurrent state is not written twice to the same effect, as keys and values are: the second run
+        # that settles a capture starts from the state this one started from
+        before = self.storage.snapshot_state([row[3] for row in prepared.ctx.host_rows]) if capturing else None
         logits = self.execute(prepared.ctx)
-        if prepared.capture and self._step_graph_limit > 0:
-            self._capture_step(prepared.ctx)
+        if capturing:
+            self._capture_step(prepared.ctx, before)
         return logits
 
     def forward(self, entries: Sequence[StepEntry], plan: StepCachePlan) -> torch.Tensor | None:
         """The step's logits, through a captured graph if this kind of step has one."""
         return self.launch(self.prepare(entries, plan))
 
-    def _capture_step(self, ctx: StepContext) -> None:
+    def _capture_step(self, ctx: StepContext, state_before=None) -> None:
         """Record the launches of a step that has just run eagerly on ``ctx``.  The step runs once
         more, on the capture stream, before it is recorded (libraries settle their per-stream
         work areas outside the capture; the same keys and values go to the same cache slots), and
@@ -411,6 +415,7 @@ class StepRunner:
         try:
             stream.wait_stream(torch.cuda.current_stream(self.device))
             with torch.cuda.stream(stream):
+                self.storage.restore_state(state_before)
                 self.model.forward(ctx)
             stream.synchronize()
             after = kernels.guarded_launch_counts()
