@@ -1090,6 +1090,192 @@ def kelasun_workload(args) -> int:
     return 0
 
 
+# ------------------------------------------- Bimolix beside Kelasun at equal layer sizes
+BIMOLIX_CHUNK, BIMOLIX_TABLE_ROWS = 1024, 32
+# FP32 multiply-adds outside the tensor cores: 148 SMs x 128 lanes x 2 flops at the 1,965 MHz the boards
+# allow (a nominal figure; the recurrence is float32 by the design's rule, so its kernel cannot use bf16 tiles)
+FP32_TFLOPS_NOMINAL = 148 * 128 * 2 * 1.965e9 / 1e12
+# (kernel of the new design, its counterpart in Kelasun) by what they do
+BIMOLIX_LIKE = (
+    ("stream_norm", "post_layer_norm", "norm + residual sum"),
+    ("qkv_prepare", "projection_norm + qkv_prepare", "q/k bias and norm, cache write"),
+    ("attention_tiles", "attention_tiles[attention]", "prompt attention"),
+    ("attention_tiles_singles", "attention_tiles_singles[attention]", "decode attention"),
+    ("retention", "attention_tiles[attention] / attention_tiles_singles[attention]", "the other token mixer"),
+    ("route_gated_act", "route_act", "routing + activation"),
+    ("gated_act", None, "act(gate) * up of the dense feed-forward"),
+)
+
+
+def bimolix_config(size: str, layers: int):
+    """Retention layers with a dense feed-forward and chunked attention layers with experts in turn: the
+    experts as many and as wide as Kelasun's at this size."""
+    from tinyvllm_b200.models import BimolixConfig
+    from tinyvllm_b200.models.bimolix import BimolixFeedForward, BimolixLayer
+
+    width, heads, kv, dim, ff = KELASUN_SIZES[size]
+    unit = kelasun_expert_width(ff)
+    experts = BimolixFeedForward(kind="moe", ff=unit, limit=7.0, experts=KELASUN_EXPERTS, top=KELASUN_TOP,
+                                 route_scale=2.5, groups=4, keep=2, shared_ff=ff - KELASUN_TOP * unit, shared_limit=7.0)
+    decay = tuple(1.0 - 2.0 ** -(5 + 4 * h / heads) for h in range(heads))
+    made = []
+    for index in range(layers):
+        if index % 2 == 0:
+            made.append(BimolixLayer(type="retention", heads=heads, dim=dim, vdim=dim, decay=decay, rot_dims=dim,
+                                     rot_base=1000000.0, mlp=BimolixFeedForward(kind="dense", ff=ff)))
+        else:
+            made.append(BimolixLayer(type="attention", heads=heads, kv_heads=kv, dim=dim, vdim=dim, scale=dim ** -0.5,
+                                     bias_max=float(BIMOLIX_CHUNK), chunk=BIMOLIX_CHUNK, mlp=experts,
+                                     rel_rows=BIMOLIX_TABLE_ROWS))
+    return BimolixConfig(vocab=MODEL["vocab_size"], width=width, norm_eps=1e-6, layers=tuple(made))
+
+
+def bimolix_roofline(name: str, size: str, tokens: int, context: int, peak: dict):
+    """(microseconds at the peaks, what bounds it) of one call of kernel ``name`` in a Bimolix layer:
+    ``tokens`` new tokens whose requests hold ``context`` tokens each (a prompt: context == tokens)."""
+    width, heads, kv, dim, ff = KELASUN_SIZES[size]
+    unit = kelasun_expert_width(ff)
+    columns = KELASUN_EXPERTS * unit + (ff - KELASUN_TOP * unit)
+    prompt = context == tokens
+    bytes_, flops, fp32 = 0.0, 0.0, 0.0
+    if name == "stream_norm":
+        bytes_ = tokens * width * (4 + 4 + 4 + 2)
+    elif name == "qkv_prepare":
+        bytes_ = tokens * dim * 2 * ((heads + kv) * 2 + kv)          # q and k in place, k and the value copy to pages
+    elif name == "attention_tiles":
+        pairs = sum(p % BIMOLIX_CHUNK + 1 for p in range(tokens))
+        flops = 2.0 * heads * 2 * dim * pairs
+    elif name == "attention_tiles_singles":
+        bytes_ = tokens * kv * (context % BIMOLIX_CHUNK + 1) * 2 * dim * 2
+    elif name == "retention":
+        fp32 = 4.0 * tokens * heads * dim * dim                      # state update and read-out, a multiply-add each
+        bytes_ = (0 if prompt else tokens) * heads * dim * dim * 4 * 2 + tokens * heads * dim * 2 * 5
+    elif name == "route_gated_act":
+        bytes_ = tokens * columns * 2 * 3
+    elif name == "gated_act":
+        bytes_ = tokens * ff * 2 * 3
+    if flops:
+        return flops / (peak["bf16_tflops"] * 1e12) * 1e6, "tensor"
+    by_memory = bytes_ / (peak["hbm_gbs"] * 1e9) * 1e6
+    by_fp32 = fp32 / (FP32_TFLOPS_NOMINAL * 1e12) * 1e6
+    return (by_fp32, "fp32 (nominal)") if by_fp32 > by_memory else (by_memory, "memory")
+
+
+def bimolix_workload(args) -> int:
+    """Prefill and decode of Bimolix at the layer sizes of the 0.6B, 8B and 32B models (random weights,
+    ``--layers`` layers, default 4: retention layers with a dense feed-forward and attention layers in
+    chunks of 1,024 with 8 experts of which 2 are used plus a shared one, in turn) beside Kelasun of the
+    same sizes: tokens/s through the engine, and every kernel of both designs with the fraction of its
+    roofline.  One JSON line."""
+    import torch
+
+    from tinyvllm_b200 import EngineConfig
+    from tinyvllm_b200.engine.engine import Engine
+    from tinyvllm_b200.engine.step import StepEntry
+
+    layers = args.layers if args.layers_given else 4
+    batch, prompt, steps, warmup = args.batch, PROMPT_TOKENS, min(args.steps, 64), max(args.warmup, 3)
+    peak, peak_source = peaks()
+    names = sorted({"stream_norm", "qkv_prepare", "attention_tiles", "attention_tiles_singles", "retention",
+                    "route_gated_act", "gated_act", "attention_rows"}
+                   | {n for pair in KELASUN_LIKE for n in pair[:1]})
+    both_kinds = ("attention_tiles", "attention_tiles_singles", "attention_rows")
+    results = []
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = [size for size in KELASUN_SIZES if not args.sizes or size in args.sizes.split(",")]
+    for size in sizes:
+        row = {"size": size}
+        for label, config in (("bimolix", bimolix_config(size, layers)), ("kelasun", kelasun_config(size, layers))):
+            with tempfile.TemporaryDirectory() as folder:
+                Path(folder, "config.json").write_text(json.dumps(config.to_json()))
+                engine = Engine.from_config(EngineConfig(
+                    model=folder, dtype="bfloat16", weights="random", seed=0, max_model_len=CONTEXT_LIMIT,
+                    max_num_seqs=batch, max_num_batched_tokens=4096, prefill_chunk_size=2048,
+                    prefill_reserve_tokens=0, prefill_reserve_requests=0, kv_block_size=16,
+                    kv_cache_memory_bytes=2 * 1024**3, graph_batch_sizes=(batch,)))
+                decode = run_decode(engine, batch, steps, warmup, sampler, prompt_tokens=prompt)
+                prefill_ms = run_prefill(engine, repeats=5, tokens=prompt)
+                runner = engine.runner
+                rng = random.Random(5)
+                with torch.inference_mode():
+                    for r in range(batch):
+                        runner.open(f"k{r}")
+                    prompts = [StepEntry(f"k{r}", tuple(random_prompt(rng, prompt)), ()) for r in range(batch)]
+
+                    def eager_step(entries):
+                        plan = runner.plan(entries)
+                        runner.execute(runner.build_context(entries, plan))
+                        runner.manager.commit(plan)
+
+                    # the GPU is kept busy (a spin kernel) while the host queues the step's launches behind it:
+                    # the events then bracket device time, not the host's pace
+                    for entry in prompts[1:]:
+                        eager_step([entry])
+                    torch.cuda.synchronize()
+                    with KernelClock(names) as clock:
+                        torch.cuda._sleep(40_000_000)
+                        eager_step([prompts[0]])
+                    torch.cuda.synchronize()
+                    by_prompt = list(clock.marks)
+                    singles = [StepEntry(f"k{r}", (1,), (0,)) for r in range(batch)]
+                    eager_step(singles)
+                    torch.cuda.synchronize()
+                    with KernelClock(names) as clock:
+                        torch.cuda._sleep(40_000_000)
+                        eager_step(singles)
+                    torch.cuda.synchronize()
+                    by_decode = list(clock.marks)
+                    for r in range(batch):
+                        runner.close(f"k{r}")
+                kernels_out = {}
+                for phase, marks, tokens in (("prefill", by_prompt, prompt), ("decode", by_decode, batch)):
+                    found, seen = {}, {}
+                    for name, start, end in marks:
+                        kind = "bimolix"
+                        if label == "kelasun":
+                            index = seen.get(name, 0)
+                            seen[name] = index + 1
+                            kind = ("attention", "latent")[index % 2] if name in both_kinds else \
+                                "latent" if name in ("latent_prepare", "rotate_heads", "head_product") else "attention"
+                        key = name if label == "bimolix" or name not in both_kinds else f"{name}[{kind}]"
+                        calls, ms, _ = found.get(key, (0, 0.0, kind))
+                        found[key] = (calls + 1, ms + start.elapsed_time(end), kind)
+                    for key, (calls, ms, kind) in sorted(found.items()):
+                        per_call = 1e3 * ms / max(1, calls)
+                        if label == "bimolix":
+                            ideal, bound = bimolix_roofline(key, size, tokens, prompt, peak)
+                        else:
+                            ideal, bound = kelasun_roofline(key.split("[")[0], kind, size, tokens, prompt, peak)
+                        kernels_out[f"{phase}:{key}"] = {
+                            "calls": calls, "us_per_call": round(per_call, 2), "roofline_us": round(ideal, 2),
+                            "bound": bound, "frac": round(ideal / per_call, 3) if per_call > 0 else None}
+                row[label] = {
+                    "decode_tokens_per_s": round(decode["tokens_per_s"], 1), "decode_ms_per_step": round(decode["ms_per_step"], 4),
+                    "prefill_tokens_per_s": round(prompt / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                    "weight_bytes": engine.runner.model.weight_bytes(), "kernels": kernels_out}
+                engine.close()
+                del engine
+                torch.cuda.empty_cache()
+        results.append(row)
+    sampler.stop()
+    print(json.dumps({
+        "metric": "Bimolix beside Kelasun of equal layer sizes: decode tok/s at batch "
+                  f"{batch} from context {prompt:,}, prefill tok/s of {prompt:,} tokens, bf16",
+        "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic (random weights and tokens)",
+        "config": {"layers": layers, "batch": batch, "vocab": MODEL["vocab_size"],
+                   "sizes": {k: list(v) for k, v in KELASUN_SIZES.items() if k in sizes},
+                   "chunk": BIMOLIX_CHUNK, "table_rows": BIMOLIX_TABLE_ROWS, "experts": KELASUN_EXPERTS,
+                   "top": KELASUN_TOP, "like_kernels": [list(pair) for pair in BIMOLIX_LIKE],
+                   "timing": "CUDA events; decode replays graphs with inputs uploaded every step, for "
+                             f"{batch} requests; kernel figures: the calls of one eager step queued behind a spin kernel, "
+                             "so that each pair of events brackets device time (warm caches)"},
+        "peaks": {"hbm_gbs": peak["hbm_gbs"], "bf16_tflops": peak["bf16_tflops"],
+                  "fp32_tflops_nominal": round(FP32_TFLOPS_NOMINAL, 1), "source": peak_source},
+        "clocks": sampler.summary(), "results": results}))
+    return 0
+
+
 def arrivals_workload(args) -> int:
     """16 requests with prompts of 64 or 512 tokens and 64 new tokens that arrive 20 ms apart, at the
     0.6B sizes, through ``Engine.submit(arrival_ns=)`` and ``Engine.step``: time to first token, time
@@ -1144,12 +1330,14 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    parser.add_argument("--workload", choices=("0.6b", "8b", "32b", "arrivals", "gumapel", "kelasun"), default="0.6b",
+    parser.add_argument("--workload", choices=("0.6b", "8b", "32b", "arrivals", "gumapel", "kelasun", "bimolix"),
+                        default="0.6b",
                         help="0.6b: the decode and prefill measurement (default); 8b, 32b: the serving "
                              "workloads of those sizes at full depth; arrivals: 16 requests 20 ms apart; "
                              "gumapel: the Gumapel design beside a windowed Qwen3 at equal layer sizes; "
-                             "kelasun: the Kelasun design beside a dense Qwen3 at equal layer sizes")
-    parser.add_argument("--sizes", default="", help="kelasun: which of 0.6b,8b,32b (default: all)")
+                             "kelasun: the Kelasun design beside a dense Qwen3 at equal layer sizes; "
+                             "bimolix: the Bimolix design beside Kelasun at equal layer sizes")
+    parser.add_argument("--sizes", default="", help="kelasun, bimolix: which of 0.6b,8b,32b (default: all)")
     parser.add_argument("--layers", type=int, default=None,
                         help="fewer layers than the configuration has (both numbers are in the line)")
     parser.add_argument("--batch", type=int, default=8)
@@ -1176,6 +1364,8 @@ def main() -> int:
         return gumapel_workload(args)
     if args.workload == "kelasun":
         return kelasun_workload(args)
+    if args.workload == "bimolix":
+        return bimolix_workload(args)
     if args.eager_profile:
         return eager_profile(args, warmup)
     return headline(args, warmup)

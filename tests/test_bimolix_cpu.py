@@ -157,3 +157,31 @@ def test_the_oracle_sees_only_its_own_chunk_and_one_more_term():
     # position 3 begins a chunk: itself and the extra term share the denominator
     assert weights[3].tolist() == [0, 0, 0, 0.5, 0, 0, 0]
     assert weights[5, 3:6].tolist() == [0.25, 0.25, 0.25]
+
+
+@pytest.mark.parametrize("name", sorted(BIMOLIX_CONFIGS))
+def test_a_table_takes_its_rows_from_the_checkpoint(name, tmp_path):
+    """config.json does not say how many rows a distance table has: a model built from it alone loads
+    tables of any number of rows, also where ``bias_max`` lies inside the linear half of the rows that
+    random weights would get."""
+    from bimolix_configs import write_folder
+    from tinyvllm_b200 import read_model_config
+
+    config = BIMOLIX_CONFIGS[name]
+    folder = write_folder(tmp_path / name, config, BIMOLIX_SEEDS[name])
+    model = Model(read_model_config(folder).to_spec(), device="cpu", dtype=torch.float32).load(folder)
+    tensors = tensors_of(config, BIMOLIX_SEEDS[name])
+    seen = 0
+    for index, layer in enumerate(config.layers):
+        if layer.type != "attention" or layer.weights_of is not None:
+            continue
+        mixer = model.blocks[model.spec.order[index].layer].mixer
+        rel = tensors[f"l{index}.mix.rel"].to(torch.bfloat16).float()
+        assert mixer.rel.shape == rel.shape
+        table = mixer.bias_table
+        assert table.shape == (math.ceil(layer.bias_max) + 1, layer.heads)
+        for distance in (0, 1, rel.shape[0] // 2, int(layer.bias_max) - 1, math.ceil(layer.bias_max)):
+            if 0 <= distance < table.shape[0]:
+                assert torch.equal(table[distance], rel[plain.distance_bucket(distance, rel.shape[0], layer.bias_max)])
+        seen += 1
+    assert seen

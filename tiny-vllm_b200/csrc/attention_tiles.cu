@@ -4,7 +4,9 @@
 // sliding window that may keep the first `keep_first` keys visible, an optional output gate (one number
 // a value, or one a head), an optional distance bias (head h takes slopes[h] * (p - j) off the score of
 // key j) and an optional sink a head (exp(sink) is added to the softmax's denominator and to nothing
-// else).  Compiled with TILES_VALUE_IN_KEY=1 the values are the first TILES_VALUE_DIM elements of the
+// else), an optional learned bias by distance (bias_table[min(p - j, rows - 1), h] is added to the scaled
+// score) and optional segments (a query sees only the keys from the start of its own segment of
+// `segment` positions, counted from position 0; not together with a window).  Compiled with TILES_VALUE_IN_KEY=1 the values are the first TILES_VALUE_DIM elements of the
 // key rows themselves (attention over latents that serve as keys and values): no value cache is read
 // and the key tile in shared memory is the value tile too.
 //
@@ -84,7 +86,20 @@ struct TileArgs {
     int num_q, num_kv, page_size, window, keep_first;
     float scale;
     const float* slopes; const float* sinks; int gate_per_head;
+    const float* bias_table; int bias_rows; int segment;
 };
+
+// The first key the query at `position` sees (kept first keys apart): the start of its segment of
+// `segment` positions counted from 0, or the far end of its window, or 0.
+__device__ __forceinline__ int lowest_seen(const TileArgs& a, int position) {
+    if (a.segment > 0) return position - position % a.segment;
+    return a.window > 0 ? max(0, position - a.window + 1) : 0;
+}
+
+// table[min(distance, rows - 1), head] in the units of the scaled scores
+__device__ __forceinline__ float table_bias(const TileArgs& a, int distance, int head) {
+    return __ldg(a.bias_table + (int64_t)min(max(distance, 0), a.bias_rows - 1) * a.num_q + head) * TL_LOG2E;
+}
 
 __device__ __forceinline__ int chunk_of_slot(int z, int window_chunks, int position, int lo, int kept);
 
@@ -119,9 +134,9 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_tiles_kernel(const
     }
     const int last_position = SINGLES ? first_position : first_position + count - 1;
     const int* table = a.block_tables + (int64_t)request * a.table_stride;
-    const int window = a.window;
-    const int lo_first = window > 0 ? max(0, first_position - window + 1) : 0;
-    const int lo_last = window > 0 ? max(0, last_position - window + 1) : 0;
+    const bool limited = a.window > 0 || a.segment > 0;
+    const int lo_first = lowest_seen(a, first_position);
+    const int lo_last = lowest_seen(a, last_position);
     const int kept = min(a.keep_first, lo_last);          // keys 0..kept-1 are seen from behind a window
 
     // ---- the key tiles this CTA walks: range A (kept first keys before the window), then range B
@@ -203,8 +218,8 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_tiles_kernel(const
     const int row_a = warp * 16 + g, row_b = row_a + 8;
     const int pos_a = SINGLES ? first_position : first_position + row_a;
     const int pos_b = SINGLES ? first_position : first_position + row_b;
-    const int lo_a = window > 0 ? max(0, pos_a - window + 1) : 0;
-    const int lo_b = window > 0 ? max(0, pos_b - window + 1) : 0;
+    const int lo_a = lowest_seen(a, pos_a);
+    const int lo_b = lowest_seen(a, pos_b);
     const int warp_pos_first = SINGLES ? first_position : first_position + warp * 16;
     const int warp_pos_last = SINGLES ? first_position : warp_pos_first + 15;
     float o_acc[VD / 8][4];
@@ -220,6 +235,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_tiles_kernel(const
     const int head_b = SINGLES ? head0 + min(row_b, count - 1) : head0;
     const float slope_a = biased ? a.slopes[head_a] * TL_LOG2E : 0.0f;
     const float slope_b = biased ? a.slopes[head_b] * TL_LOG2E : 0.0f;
+    const bool tabled = a.bias_table != nullptr;
 
     for (int t = 0; t < tiles; ++t) {
         const int buffer = t & 1;
@@ -230,7 +246,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_tiles_kernel(const
         const int key0 = key_of_tile(t);
         // nothing of this tile for this warp's rows: past their diagonal, or before their windows and not kept
         const bool none = key0 > warp_pos_last ||
-                          (window > 0 && key0 + TL_BN - 1 < max(0, warp_pos_first - window + 1) && key0 >= a.keep_first);
+                          (limited && key0 + TL_BN - 1 < lowest_seen(a, warp_pos_first) && key0 >= a.keep_first);
         if (!busy || none) continue;
 
         const bf16* k_tile = k_s + buffer * TL_BN * KROW;
@@ -258,7 +274,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_tiles_kernel(const
 
         // every row of the warp sees every key of the tile: below all diagonals and inside all windows
         const bool full = key0 + TL_BN - 1 <= warp_pos_first &&
-                          (window <= 0 || key0 >= max(0, warp_pos_last - window + 1));
+                          (!limited || key0 >= lowest_seen(a, warp_pos_last));
         float tile_max_a = -INFINITY, tile_max_b = -INFINITY;
 #pragma unroll
         for (int n = 0; n < TL_BN / 8; ++n) {
@@ -268,6 +284,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_tiles_kernel(const
                 const bool upper = i < 2;
                 float s = s_acc[n][i] * scale_log2;
                 if (biased) s -= (upper ? slope_a : slope_b) * (float)((upper ? pos_a : pos_b) - key);
+                if (tabled) s += table_bias(a, (upper ? pos_a : pos_b) - key, upper ? head_a : head_b);
                 if (!full) {
                     const int pos = upper ? pos_a : pos_b, lo = upper ? lo_a : lo_b;
                     if (!(key <= pos && (key >= lo || key < a.keep_first))) s = -INFINITY;
@@ -427,7 +444,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_singles_kernel(con
     const int request = a.token_row[token], position = a.positions[token];
     if (request < 0 || position < 0) return;                 // a padding row; the merge writes its zeros
     const int group = a.num_q / a.num_kv, kv_head = blockIdx.y, head0 = kv_head * group;
-    const int lo = a.window > 0 ? max(0, position - a.window + 1) : 0;
+    const int lo = lowest_seen(a, position);
     const int kept = min(a.keep_first, lo);
     const int chunk = chunk_of_slot(blockIdx.z, a.window_chunks, position, lo, kept);
     if (chunk < 0) return;
@@ -509,6 +526,7 @@ __global__ void __launch_bounds__(TL_WARPS * 32, 3) attention_singles_kernel(con
                 const int key = tile_key + n * 8 + 2 * t4 + (i & 1);
                 float s = s_acc[n][i] * scale_log2;
                 if (biased) s -= (i < 2 ? slope_a : slope_b) * (float)(position - key);
+                if (a.bias_table) s += table_bias(a, position - key, head0 + min(i < 2 ? g : g + 8, group - 1));
                 if (!(key <= position && (key >= lo || key < kept))) s = -INFINITY;
                 s_acc[n][i] = s;
                 if (i < 2) m_a = fmaxf(m_a, s); else m_b = fmaxf(m_b, s);
@@ -611,7 +629,7 @@ __global__ void merge_singles_kernel(const TileArgs a, int tokens) {
         for (int dim = lane; dim < VD; dim += 32) dst[dim] = __float2bfloat16_rn(0.0f);
         return;
     }
-    const int lo = a.window > 0 ? max(0, position - a.window + 1) : 0;
+    const int lo = lowest_seen(a, position);
     const int kept = min(a.keep_first, lo);
     const int own = position / TL_CHUNK, first_chunk = lo / TL_CHUNK;
     const int slots = a.window_chunks + a.kept_chunks;
@@ -676,6 +694,7 @@ static size_t tiles_shared_bytes() {
 }
 
 static int check_common(const TileArgs& a, int key_dim, int value_dim) {
+    if (a.segment < 0 || (a.segment > 0 && a.window > 0) || (a.bias_table && a.bias_rows <= 0)) return TVB_BAD_ARGUMENT;
     if (key_dim != TILES_KEY_DIM || value_dim != TILES_VALUE_DIM || TILES_KEY_DIM % 16 || TILES_VALUE_DIM % 16 ||
         a.num_q <= 0 || a.num_kv <= 0 || a.num_q % a.num_kv || a.page_size <= 0 || a.window < 0 || a.keep_first < 0 ||
         (a.q_token_stride * 2) % 16 || ((uintptr_t)a.q) % 16 || a.out_token_stride % 2 || ((uintptr_t)a.out) % 4 ||
@@ -688,6 +707,30 @@ static int check_common(const TileArgs& a, int key_dim, int value_dim) {
 // Prompt portions: tile i holds tile_count[i] (1..64) consecutive tokens from flat index tile_first[i]
 // on, of the request in row tile_row[i] of block_tables.
 // `slopes` and `sinks`: float32 [num_q] or null; `gate_per_head`: the gate holds one number a head.
+// `bias_table`: float32 [bias_rows, num_q] or null; `segment`: 0 for none.
+extern "C" int tvb_attention_tiles_table(const void* q, long long q_token_stride, const void* key_cache,
+                                         const void* value_cache, const int* block_tables, int table_stride,
+                                         const int* positions, const int* tile_row, const int* tile_first,
+                                         const int* tile_count, void* out, long long out_token_stride,
+                                         const void* gate, long long gate_token_stride, int gate_per_head,
+                                         const float* slopes, const float* sinks, const float* bias_table,
+                                         int bias_rows, int segment, int tiles, int num_q, int num_kv,
+                                         int key_dim, int value_dim, int page_size, int window, int keep_first,
+                                         float scale, void* stream) {
+    if (tiles <= 0) return 0;
+    TileArgs a{(const bf16*)q, q_token_stride, (const bf16*)key_cache, (const bf16*)value_cache, block_tables,
+               table_stride, positions, nullptr, tile_row, tile_first, tile_count, (bf16*)out, out_token_stride,
+               (const bf16*)gate, gate_token_stride, nullptr, 0, 0, num_q, num_kv, page_size, window,
+               window > 0 ? keep_first : 0, scale, slopes, sinks, gate_per_head, bias_table, bias_rows, segment};
+    if (check_common(a, key_dim, value_dim) || num_q > 65535) return TVB_BAD_ARGUMENT;
+    auto kernel = attention_tiles_kernel<TILES_KEY_DIM, TILES_VALUE_DIM, false>;
+    const size_t shared = tiles_shared_bytes();
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    if (e != cudaSuccess) return (int)e;
+    kernel<<<dim3(tiles, num_q), TL_WARPS * 32, shared, (cudaStream_t)stream>>>(a);
+    return tvb_last_error();
+}
+
 extern "C" int tvb_attention_tiles_biased(const void* q, long long q_token_stride, const void* key_cache,
                                           const void* value_cache, const int* block_tables, int table_stride,
                                           const int* positions, const int* tile_row, const int* tile_first,
@@ -696,18 +739,10 @@ extern "C" int tvb_attention_tiles_biased(const void* q, long long q_token_strid
                                           const float* slopes, const float* sinks, int tiles, int num_q, int num_kv,
                                           int key_dim, int value_dim, int page_size, int window, int keep_first,
                                           float scale, void* stream) {
-    if (tiles <= 0) return 0;
-    TileArgs a{(const bf16*)q, q_token_stride, (const bf16*)key_cache, (const bf16*)value_cache, block_tables,
-               table_stride, positions, nullptr, tile_row, tile_first, tile_count, (bf16*)out, out_token_stride,
-               (const bf16*)gate, gate_token_stride, nullptr, 0, 0, num_q, num_kv, page_size, window,
-               window > 0 ? keep_first : 0, scale, slopes, sinks, gate_per_head};
-    if (check_common(a, key_dim, value_dim) || num_q > 65535) return TVB_BAD_ARGUMENT;
-    auto kernel = attention_tiles_kernel<TILES_KEY_DIM, TILES_VALUE_DIM, false>;
-    const size_t shared = tiles_shared_bytes();
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-    if (e != cudaSuccess) return (int)e;
-    kernel<<<dim3(tiles, num_q), TL_WARPS * 32, shared, (cudaStream_t)stream>>>(a);
-    return tvb_last_error();
+    return tvb_attention_tiles_table(q, q_token_stride, key_cache, value_cache, block_tables, table_stride, positions,
+                                     tile_row, tile_first, tile_count, out, out_token_stride, gate, gate_token_stride,
+                                     gate_per_head, slopes, sinks, nullptr, 0, 0, tiles, num_q, num_kv, key_dim,
+                                     value_dim, page_size, window, keep_first, scale, stream);
 }
 
 extern "C" int tvb_attention_tiles(const void* q, long long q_token_stride, const void* key_cache,
@@ -732,6 +767,7 @@ static void singles_chunks(int window, int keep_first, int max_context, int* win
     *kept_chunks = (keep_first + TL_CHUNK - 1) / TL_CHUNK;
 }
 
+// `window`: with segments, the segment's size (a segment touches the chunks a window of its size can).
 extern "C" long long tvb_attention_tiles_singles_floats(int tokens, int num_q, int window, int keep_first,
                                                          int max_context) {
     int wc, kc;
@@ -741,22 +777,23 @@ extern "C" long long tvb_attention_tiles_singles_floats(int tokens, int num_q, i
 
 // Single tokens (decoded ones): token i is of the request in row token_row[i] (-1: padding) at
 // positions[i] < max_context; its keys and values are in the cache already.
-extern "C" int tvb_attention_tiles_singles_biased(const void* q, long long q_token_stride, const void* key_cache,
-                                                  const void* value_cache, const int* block_tables, int table_stride,
-                                                  const int* positions, const int* token_row, void* out,
-                                                  long long out_token_stride, const void* gate,
-                                                  long long gate_token_stride, int gate_per_head, const float* slopes,
-                                                  const float* sinks, float* scratch, int tokens, int num_q,
-                                                  int num_kv, int key_dim, int value_dim, int page_size, int window,
-                                                  int keep_first, float scale, int max_context, void* stream) {
+extern "C" int tvb_attention_tiles_singles_table(const void* q, long long q_token_stride, const void* key_cache,
+                                                 const void* value_cache, const int* block_tables, int table_stride,
+                                                 const int* positions, const int* token_row, void* out,
+                                                 long long out_token_stride, const void* gate,
+                                                 long long gate_token_stride, int gate_per_head, const float* slopes,
+                                                 const float* sinks, const float* bias_table, int bias_rows,
+                                                 int segment, float* scratch, int tokens, int num_q,
+                                                 int num_kv, int key_dim, int value_dim, int page_size, int window,
+                                                 int keep_first, float scale, int max_context, void* stream) {
     if (tokens <= 0) return 0;
     TileArgs a{(const bf16*)q, q_token_stride, (const bf16*)key_cache, (const bf16*)value_cache, block_tables,
                table_stride, positions, token_row, nullptr, nullptr, nullptr, (bf16*)out, out_token_stride,
                (const bf16*)gate, gate_token_stride, scratch, 0, 0, num_q, num_kv, page_size, window,
-               window > 0 ? keep_first : 0, scale, slopes, sinks, gate_per_head};
+               window > 0 ? keep_first : 0, scale, slopes, sinks, gate_per_head, bias_table, bias_rows, segment};
     if (check_common(a, key_dim, value_dim) || !scratch || max_context <= 0 || num_q / num_kv > TL_BM || num_kv > 65535)
         return TVB_BAD_ARGUMENT;
-    singles_chunks(a.window, a.keep_first, max_context, &a.window_chunks, &a.kept_chunks);
+    singles_chunks(a.segment > 0 ? a.segment : a.window, a.keep_first, max_context, &a.window_chunks, &a.kept_chunks);
     if (a.window_chunks + a.kept_chunks > 65535) return TVB_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(tokens, num_kv, a.window_chunks + a.kept_chunks);
@@ -778,6 +815,21 @@ extern "C" int tvb_attention_tiles_singles_biased(const void* q, long long q_tok
     const int64_t rows = (int64_t)tokens * num_q;
     merge_singles_kernel<TILES_VALUE_DIM><<<(unsigned)((rows + TL_WARPS - 1) / TL_WARPS), TL_WARPS * 32, 0, s>>>(a, tokens);
     return tvb_last_error();
+}
+
+extern "C" int tvb_attention_tiles_singles_biased(const void* q, long long q_token_stride, const void* key_cache,
+                                                  const void* value_cache, const int* block_tables, int table_stride,
+                                                  const int* positions, const int* token_row, void* out,
+                                                  long long out_token_stride, const void* gate,
+                                                  long long gate_token_stride, int gate_per_head, const float* slopes,
+                                                  const float* sinks, float* scratch, int tokens, int num_q,
+                                                  int num_kv, int key_dim, int value_dim, int page_size, int window,
+                                                  int keep_first, float scale, int max_context, void* stream) {
+    return tvb_attention_tiles_singles_table(q, q_token_stride, key_cache, value_cache, block_tables, table_stride,
+                                             positions, token_row, out, out_token_stride, gate, gate_token_stride,
+                                             gate_per_head, slopes, sinks, nullptr, 0, 0, scratch, tokens, num_q,
+                                             num_kv, key_dim, value_dim, page_size, window, keep_first, scale,
+                                             max_context, stream);
 }
 
 extern "C" int tvb_attention_tiles_singles(const void* q, long long q_token_stride, const void* key_cache,

@@ -322,13 +322,14 @@ def windowed_attention(ctx, mixer, projected: torch.Tensor, at: int, run: int, o
     queries = projected[:, q_at:q_at + mixer.q_cols]
     heads = dict(num_q=mixer.num_heads, num_kv=mixer.num_kv_heads, key_dim=mixer.key_dim,
                  value_dim=mixer.value_dim, window=mixer.window, keep_first=mixer.keep_first, scale=mixer.scale,
-                 gate_per_head=mixer.gate == "head", slopes=mixer.slopes, sinks=mixer.sinks)
-    if bias_table is None and segment is None and windowed_on_tensor_cores(mixer, projected, q_at, g_at, out):
+                 gate_per_head=mixer.gate == "head", slopes=mixer.slopes, sinks=mixer.sinks,
+                 bias_table=bias_table, segment=segment)
+    if not (segment and mixer.window) and windowed_on_tensor_cores(mixer, projected, q_at, g_at, out):
         # bfloat16: prompt portions in tiles of 64 tokens, single tokens (decoded ones, whose keys are in the
         # cache by now) one CTA per kv head and chunk of keys
         def singles(part):
             need = kernels.attention_tiles_singles_floats(
-                part.stop - part.start, mixer.num_heads, mixer.value_dim, mixer.window, mixer.keep_first,
+                part.stop - part.start, mixer.num_heads, mixer.value_dim, segment or mixer.window, mixer.keep_first,
                 ctx.max_context)
             kernels.attention_tiles_singles(
                 queries[part], keys, values, ctx.block_tables[group], ctx.positions[part], ctx.token_row[part],

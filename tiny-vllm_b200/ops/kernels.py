@@ -970,12 +970,22 @@ def _tiles_common(name, q, key_cache, value_cache, out, gate, num_q, num_kv, key
     return value_in_key
 
 
+def _tiles_table(who: str, bias_table, segment, window, num_q: int) -> None:
+    if bias_table is not None and (bias_table.dtype != torch.float32 or bias_table.dim() != 2
+                                   or bias_table.shape[1] != num_q or bias_table.shape[0] < 1
+                                   or not bias_table.is_contiguous()):
+        raise KernelError(f"{who}: the bias table must be contiguous float32 [distances, num_q]")
+    if segment is not None and (segment <= 0 or window):
+        raise KernelError(f"{who}: a segment holds at least one position and comes without a window")
+
+
 def attention_tiles(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor | None,
                     block_tables: torch.Tensor, positions: torch.Tensor, tile_row: torch.Tensor,
                     tile_first: torch.Tensor, tile_count: torch.Tensor, *, num_q: int, num_kv: int,
                     key_dim: int, value_dim: int, window: int | None, keep_first: int, scale: float,
                     out: torch.Tensor, gate: torch.Tensor | None = None, gate_per_head: bool = False,
-                    slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None) -> torch.Tensor:
+                    slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None,
+                    bias_table: torch.Tensor | None = None, segment: int | None = None) -> torch.Tensor:
     """Windowed paged attention on the tensor cores for tiles of up to 64 consecutive query tokens of
     one request (bfloat16; float32 scores, weights and sums).  ``q`` [tokens, >= num_q * key_dim]
     (rows may be strided) holds prepared queries; tile i holds ``tile_count[i]`` tokens from flat
@@ -983,10 +993,13 @@ def attention_tiles(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch
     ``keep_first`` keys stay visible.  ``gate``: the output is multiplied by sigmoid(gate), one number a
     value or (``gate_per_head``, [tokens, num_q]) one a head.  ``slopes`` (float32 [num_q]): slope *
     (position - j) is taken off the score of key j; ``sinks`` (float32 [num_q]): exp(sink) joins the
-    denominator once.  ``value_cache=None``: the values are the first ``value_dim`` elements of the key
+    denominator once.  ``bias_table`` (float32 [rows, num_q]): table[min(position - j, rows - 1), head] is
+    added to the score of key j; ``segment`` (not with a window): the query at position p sees only the keys
+    from p - p % segment on.  ``value_cache=None``: the values are the first ``value_dim`` elements of the key
     rows."""
     _need_cuda(q, key_cache, value_cache, block_tables, positions, tile_row, tile_first, tile_count, out, gate,
-               slopes, sinks)
+               slopes, sinks, bias_table)
+    _tiles_table("attention_tiles", bias_table, segment, window, num_q)
     tokens, tiles = positions.shape[0], tile_row.shape[0]
     value_in_key = _tiles_common("attention_tiles", q, key_cache, value_cache, out, gate, num_q, num_kv, key_dim,
                                  value_dim, tokens, gate_per_head, slopes, sinks)
@@ -996,15 +1009,15 @@ def attention_tiles(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch
     library = _tiles_library(key_dim, value_dim, value_in_key)
     if _fn_of(library, "tvb_attention_tiles_tile_tokens", [])() != PREFILL_TILE_TOKENS:
         raise KernelError("attention_tiles: the library's tile size is not the one steps are cut for")
-    fn = _fn_of(library, "tvb_attention_tiles_biased",
+    fn = _fn_of(library, "tvb_attention_tiles_table",
                 [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                 c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p] + [c_int] * 8
+                 c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 10
                 + [c_float, c_void_p])
     _check(fn(q.data_ptr(), q.stride(0), key_cache.data_ptr(), _ptr(value_cache), block_tables.data_ptr(),
               block_tables.shape[1], positions.data_ptr(), tile_row.data_ptr(), tile_first.data_ptr(),
               tile_count.data_ptr(), out.data_ptr(), out.stride(0), _ptr(gate), 0 if gate is None else gate.stride(0),
-              1 if gate_per_head else 0, _ptr(slopes), _ptr(sinks),
-              tiles, num_q, num_kv, key_dim, value_dim, key_cache.shape[2], window or 0, keep_first if window else 0,
+              1 if gate_per_head else 0, _ptr(slopes), _ptr(sinks), _ptr(bias_table),
+              0 if bias_table is None else bias_table.shape[0], segment or 0, tiles, num_q, num_kv, key_dim, value_dim, key_cache.shape[2], window or 0, keep_first if window else 0,
               scale, _stream()), "attention_tiles")
     return out
 
@@ -1014,27 +1027,32 @@ def attention_tiles_singles(q: torch.Tensor, key_cache: torch.Tensor, value_cach
                             num_q: int, num_kv: int, key_dim: int, value_dim: int, window: int | None,
                             keep_first: int, scale: float, max_context: int, scratch: torch.Tensor,
                             out: torch.Tensor, gate: torch.Tensor | None = None, gate_per_head: bool = False,
-                            slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None) -> torch.Tensor:
+                            slopes: torch.Tensor | None = None, sinks: torch.Tensor | None = None,
+                            bias_table: torch.Tensor | None = None, segment: int | None = None) -> torch.Tensor:
     """The same attention for single tokens whose keys and values are in the cache already (decoded
     tokens): a CTA serves the q heads of one kv head over one chunk of 128 keys, a second launch
     merges a row's chunks.  Token i is of request row ``token_row[i]`` (-1: padding, zeros come out)
     at ``positions[i]`` < ``max_context``; ``scratch``: float32, :func:`attention_tiles_singles_floats`."""
-    _need_cuda(q, key_cache, value_cache, block_tables, positions, token_row, out, gate, scratch, slopes, sinks)
+    _need_cuda(q, key_cache, value_cache, block_tables, positions, token_row, out, gate, scratch, slopes, sinks,
+               bias_table)
+    _tiles_table("attention_tiles_singles", bias_table, segment, window, num_q)
     tokens = positions.shape[0]
     value_in_key = _tiles_common("attention_tiles_singles", q, key_cache, value_cache, out, gate, num_q, num_kv,
                                  key_dim, value_dim, tokens, gate_per_head, slopes, sinks)
     for t in (block_tables, positions, token_row):
         if t.dtype != torch.int32 or not t.is_contiguous():
             raise KernelError("attention_tiles_singles: index tensors must be contiguous int32")
-    need = attention_tiles_singles_floats(tokens, num_q, value_dim, window, keep_first, max_context)
+    need = attention_tiles_singles_floats(tokens, num_q, value_dim, segment or window, keep_first, max_context)
     if scratch.dtype != torch.float32 or scratch.numel() < need:
         raise KernelError(f"attention_tiles_singles needs {need} float32 of scratch")
-    fn = _fn_of(_tiles_library(key_dim, value_dim, value_in_key), "tvb_attention_tiles_singles_biased",
+    fn = _fn_of(_tiles_library(key_dim, value_dim, value_in_key), "tvb_attention_tiles_singles_table",
                 [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong,
-                 c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 8 + [c_float, c_int, c_void_p])
+                 c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p] + [c_int] * 8
+                + [c_float, c_int, c_void_p])
     _check(fn(q.data_ptr(), q.stride(0), key_cache.data_ptr(), _ptr(value_cache), block_tables.data_ptr(),
               block_tables.shape[1], positions.data_ptr(), token_row.data_ptr(), out.data_ptr(), out.stride(0),
               _ptr(gate), 0 if gate is None else gate.stride(0), 1 if gate_per_head else 0, _ptr(slopes), _ptr(sinks),
+              _ptr(bias_table), 0 if bias_table is None else bias_table.shape[0], segment or 0,
               scratch.data_ptr(), tokens, num_q, num_kv, key_dim,
               value_dim, key_cache.shape[2], window or 0, keep_first if window else 0, scale, max_context,
               _stream()), "attention_tiles_singles", 2)

@@ -174,9 +174,13 @@ class WindowedAttention(Part):
         if segment is not None and segment <= 0:
             raise ValueError("a segment holds at least one position")
         if distance_table is not None:
+            # the checkpoint's table decides the rows (finalize checks those against ``far``); the count given
+            # here only sizes random weights, and gives way where ``far`` lies inside its linear half
             rows, far = int(distance_table[0]), float(distance_table[1])
-            if rows < 2 or not far > rows // 2:
-                raise ValueError("a distance table has at least two rows and reaches beyond its linear half")
+            if rows < 2 or not far > 1.0:
+                raise ValueError("a distance table has at least two rows and reaches beyond distance 1")
+            while rows > 2 and not far > rows // 2:
+                rows -= 1
             distance_table = (rows, far)
         self.qk_bias, self.values_are_keys = bool(qk_bias), bool(values_are_keys)
         self.distance_table, self.segment = distance_table, segment
@@ -317,8 +321,8 @@ class WindowedAttention(Part):
         kernel or the tensor-core kernel for single tokens asks for, whichever is more."""
         span = chunks * kernels.attention_chunk_keys()
         return max(kernels.attention_rows_scratch_floats(rows, self.num_heads, self.value_dim, chunks),
-                   kernels.attention_tiles_singles_floats(rows, self.num_heads, self.value_dim, self.window,
-                                                          self.keep_first, span))
+                   kernels.attention_tiles_singles_floats(rows, self.num_heads, self.value_dim,
+                                                          self.segment or self.window, self.keep_first, span))
 
     # ---------------------------------------------------------------- running
     def between(self, projected, at: int, ctx, out, run: int) -> None:
