@@ -100,30 +100,44 @@ def test_retention_from_a_carried_state(heads, dim, vdim, rot, gate, dtype):
         want_state[slot] = left
         first += length
     want = torch.cat(want)
-    device_state = state.to(CUDA)
     row_starts = [0]
     for length in lengths:
         row_starts.append(row_starts[-1] + length)
     inv_freq = torch.tensor([base ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=F64).float().to(CUDA) if rot else None
-    raw = torch.empty(tokens, heads * vdim, dtype=torch.float32, device=CUDA)
-    got = kernels.retention(
-        proj.to(dtype).to(CUDA), q_at=q_at, k_at=k_at, v_at=v_at, g_at=None if gate is None else g_at, heads=heads,
-        dim=dim, vdim=vdim, decay=torch.tensor(decay, dtype=torch.float32, device=CUDA), state=device_state,
-        row_starts=ints(row_starts), state_slots=ints(slots),
-        token_row=ints([r for r, n in enumerate(lengths) for _ in range(n)]),
-        positions=ints([s + i for s, n in zip(starts, lengths) for i in range(n)]), inv_freq=inv_freq, rot_dims=rot,
-        pairing="half_split", key_scale=dim ** -0.5, unit_norm=True, eps=eps, gate_act=gate, raw_out=raw)
-    # float32 angles at position 400 are off by 3e-5 of a radian against float64 ones
-    limit = (2e-4 if rot else 2e-5) if dtype == torch.float32 else None
-    close(got, want, dtype, limit=limit)
-    close(device_state, want_state, torch.float32, limit=2e-4 if rot else 2e-5)
-    # the far key carries: without decay its value is most of what head 0 reads at the last token of the portion
-    if far_key:
-        v2 = proj[2, v_at:v_at + vdim]
-        o = raw[402, :vdim].double().cpu()
-        assert (o @ v2) / (o.norm() * v2.norm()) > 0.8
-    untouched = [s for s in range(6) if s not in slots]
-    assert torch.equal(device_state[untouched].cpu(), state[untouched])
+    # every number of lanes a column of the state that the key size takes, and the kernel's own choice (0)
+    # ... as whole entries (0), in pieces of 5, 64 and 403 tokens (the long entry is one piece, 81 or 7, the
+    # single tokens a piece each), and as the wrapper chooses for a step of this size
+    ways = [(lanes, 0) for lanes in [0] + [n for n in (4, 8, 16, 32) if n == 4 or n <= -(-dim // 4)]]
+    ways += [(0, 5), (4, 64), (0, 403), (0, None)]
+    for lanes, segment in ways:
+        device_state = state.to(CUDA)
+        raw = torch.empty(tokens, heads * vdim, dtype=torch.float32, device=CUDA)
+        got = kernels.retention(
+            proj.to(dtype).to(CUDA), q_at=q_at, k_at=k_at, v_at=v_at, g_at=None if gate is None else g_at, heads=heads,
+            dim=dim, vdim=vdim, decay=torch.tensor(decay, dtype=torch.float32, device=CUDA), state=device_state,
+            row_starts=ints(row_starts), state_slots=ints(slots),
+            token_row=ints([r for r, n in enumerate(lengths) for _ in range(n)]),
+            positions=ints([s + i for s, n in zip(starts, lengths) for i in range(n)]), inv_freq=inv_freq, rot_dims=rot,
+            pairing="half_split", key_scale=dim ** -0.5, unit_norm=True, eps=eps, gate_act=gate, raw_out=raw, lanes=lanes,
+            segment=segment)
+        # float32 angles at position 400 are off by 3e-5 of a radian against float64 ones
+        limit = (2e-4 if rot else 2e-5) if dtype == torch.float32 else None
+        close(got, want, dtype, limit=limit)
+        close(device_state, want_state, torch.float32, limit=2e-4 if rot else 2e-5)
+        # the far key carries: without decay its value is most of what head 0 reads at the last token of the portion
+        if far_key:
+            v2 = proj[2, v_at:v_at + vdim]
+            o = raw[402, :vdim].double().cpu()
+            assert (o @ v2) / (o.norm() * v2.norm()) > 0.8
+        untouched = [s for s in range(6) if s not in slots]
+        assert torch.equal(device_state[untouched].cpu(), state[untouched])
+    with pytest.raises(kernels.KernelError):      # more lanes than the key has float4s
+        kernels.retention(
+            proj.to(dtype).to(CUDA), q_at=q_at, k_at=k_at, v_at=v_at, g_at=None, heads=heads, dim=dim, vdim=vdim,
+            decay=torch.tensor(decay, dtype=torch.float32, device=CUDA), state=state.to(CUDA),
+            row_starts=ints(row_starts), state_slots=ints(slots),
+            token_row=ints([r for r, n in enumerate(lengths) for _ in range(n)]),
+            positions=ints([s + i for s, n in zip(starts, lengths) for i in range(n)]), key_scale=1.0, lanes=64)
 
 
 def paged(keys, values, page, dtype, seed, fill):

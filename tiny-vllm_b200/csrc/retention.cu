@@ -10,8 +10,8 @@
 //                       or (2i, 2i + 1)), k then multiplied by `key_scale`
 //   retention_scan      the recurrence itself, token by token from the state the request's earlier
 //                       tokens left (a slot of the state arena) to the state its next tokens start
-//                       from; a CTA has one (request, head, 32 value columns), a thread a quarter of
-//                       one column of the state in registers; tokens come in blocks of eight through
+//                       from; a CTA has one (request, head, 128 / lanes value columns), a thread one
+//                       of `lanes` parts of a column of the state in registers; tokens come in blocks of eight through
 //                       shared memory, the next block's loads in flight while this one is computed
 //   retention_finish    every head's o divided by its root mean square (or not), times act(gate),
 //                       rounded once to the storage type
@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(128) retention_prepare_kernel(
     const float* __restrict__ inv_freq, int rot_dims, int pairing, float key_scale,
     const int* __restrict__ positions, float* __restrict__ q_out, float* __restrict__ k_out) {
     __shared__ float cos_s[RET_MAX_TURNED], sin_s[RET_MAX_TURNED];
-    const int token = blockIdx.x;
+    const int token = blockIdx.x;                 // block y: a slice of the row's q and k elements
     const int half = inv_freq ? rot_dims >> 1 : 0;
     const float position = (float)max(positions[token], 0);
     for (int j = threadIdx.x; j < half; j += blockDim.x)
@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(128) retention_prepare_kernel(
     __syncthreads();
     const T* row = proj + (int64_t)token * token_stride;
     const int per = heads * dim;
-    for (int e = threadIdx.x; e < 2 * per; e += blockDim.x) {
+    for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < 2 * per; e += gridDim.y * blockDim.x) {
         const bool is_key = e >= per;
         const int inside = is_key ? e - per : e;
         const int i = inside % dim;
@@ -59,73 +59,108 @@ __global__ void __launch_bounds__(128) retention_prepare_kernel(
 }
 
 #define RET_THREADS 128
-#define RET_GROUPS 4                              // threads that share a column of the state
-#define RET_COLS (RET_THREADS / RET_GROUPS)       // value columns a CTA
 #define RET_BLOCK 8                               // tokens that wait in shared memory
 
-// ROWS: rows of the state a thread holds (dim <= RET_GROUPS * ROWS)
-template <typename T, int ROWS>
+// GROUPS: lanes that share a column of the state (a power of two up to 32); a CTA has
+// RET_THREADS / GROUPS value columns.  ROWS: rows of the state a thread holds, a multiple of four
+// (dim <= GROUPS * ROWS): rows 4 (group + GROUPS j) .. + 3 for j = 0 .. ROWS / 4 - 1, so that the lanes of
+// a column read neighbouring float4s of a token's q and k.  The host takes more lanes a column where
+// few (request, head) pairs would leave SMs idle: a long prompt alone runs on GROUPS = 16 or 32.
+template <typename T, int GROUPS, int ROWS, bool CORRECT>
 __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const T* __restrict__ v, int64_t v_stride,
     float* __restrict__ state, const float* __restrict__ decay, const int* __restrict__ row_starts,
     const int* __restrict__ state_slots, const int* __restrict__ token_row, float* __restrict__ out,
-    int heads, int dim, int vdim) {
-    constexpr int LOADS = RET_BLOCK * RET_GROUPS * ROWS / RET_THREADS;      // q (and k) values a thread fetches a block
-    __shared__ float q_s[RET_BLOCK][RET_GROUPS * ROWS];
-    __shared__ float k_s[RET_BLOCK][RET_GROUPS * ROWS];
-    __shared__ float v_s[RET_BLOCK][RET_COLS];
-    const int row = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * RET_COLS;
-    const int tid = threadIdx.x, group = tid % RET_GROUPS, col = tid / RET_GROUPS;
-    const int begin = row_starts[row], count = row_starts[row + 1] - begin;
+    float* __restrict__ parts, int segment, int rows, int heads, int dim, int vdim) {
+    constexpr int COLS = RET_THREADS / GROUPS;
+    constexpr int WIDTH = GROUPS * ROWS;
+    constexpr int LOADS = RET_BLOCK * WIDTH / RET_THREADS;                  // q (and k) values a thread fetches a block
+    constexpr int V_LOADS = (RET_BLOCK * COLS + RET_THREADS - 1) / RET_THREADS;
+    static_assert(ROWS % 4 == 0 && LOADS >= 1 && RET_BLOCK * WIDTH % RET_THREADS == 0, "retention_scan: tile");
+    __shared__ __align__(16) float q_s[RET_BLOCK][WIDTH];
+    __shared__ __align__(16) float k_s[CORRECT ? 1 : RET_BLOCK][CORRECT ? 4 : WIDTH];
+    __shared__ float v_s[CORRECT ? 1 : RET_BLOCK][COLS];
+    __shared__ float power_s[RET_BLOCK];
+    const int head = blockIdx.y, col0 = blockIdx.z * COLS;
+    const int tid = threadIdx.x, group = tid % GROUPS, col = tid / GROUPS;
+    // whole entries (segment == 0: block x is the entry) or pieces of `segment` tokens (block x is the
+    // piece, counted through the entries in order)
+    int row = blockIdx.x, begin, count;
+    if (segment <= 0) {
+        begin = row_starts[row];
+        count = row_starts[row + 1] - begin;
+    } else {
+        int before = 0, tokens = 0;
+        for (row = 0; row < rows; ++row) {
+            tokens = row_starts[row + 1] - row_starts[row];
+            const int pieces = (tokens + segment - 1) / segment;
+            if ((int)blockIdx.x < before + pieces) break;
+            before += pieces;
+        }
+        if (row == rows) return;                  // the grid is as large as the pieces can be many
+        const int piece = blockIdx.x - before;
+        begin = row_starts[row] + piece * segment;
+        count = min(segment, tokens - piece * segment);
+    }
     if (count <= 0) return;
     const int c = col0 + col;
     const bool live = c < vdim;
     if (token_row[begin] < 0) {                   // a padding row of a recorded batch: no request, no state
-        if (live && group == 0)
+        if (!CORRECT && live && group == 0)
             for (int t = 0; t < count; ++t) out[(int64_t)(begin + t) * heads * vdim + (int64_t)head * vdim + c] = 0.0f;
         return;
     }
     const float a = decay[head];
-    float* mine = state + (((int64_t)state_slots[row] * heads + head) * dim) * vdim + c;
+    // whole entries start from and leave the request's state; a piece starts from nothing and leaves what
+    // its tokens add (`parts`), which the combine kernel turns into the state the piece starts from: the
+    // correcting pass reads that and adds what it gives to every token of the piece
+    float* mine = (segment <= 0 ? state + (((int64_t)state_slots[row] * heads + head) * dim) * vdim
+                                : parts + (((int64_t)blockIdx.x * heads + head) * dim) * vdim) + c;
     float s[ROWS];
+    bool any = false;
 #pragma unroll
     for (int i = 0; i < ROWS; ++i) {
-        const int d = group + RET_GROUPS * i;
-        s[i] = (live && d < dim) ? mine[(int64_t)d * vdim] : 0.0f;
+        const int d = 4 * (group + GROUPS * (i >> 2)) + (i & 3);
+        s[i] = (live && d < dim && (segment <= 0 || CORRECT)) ? mine[(int64_t)d * vdim] : 0.0f;
+        any = any || s[i] != 0.0f;
     }
+    if (CORRECT && !__syncthreads_or(any)) return;            // the request's first piece: nothing came before
     const int64_t qk_stride = (int64_t)heads * dim;
     const float* q_head = q + (int64_t)begin * qk_stride + (int64_t)head * dim;
     const float* k_head = k + (int64_t)begin * qk_stride + (int64_t)head * dim;
     const T* v_head = v + (int64_t)begin * v_stride + (int64_t)head * vdim + col0;
-    const int width = RET_GROUPS * ROWS;
-    float q_next[LOADS], k_next[LOADS], v_next[2];
+    float q_next[LOADS], k_next[LOADS], v_next[V_LOADS];
 
     auto fetch = [&](int first) {                 // tokens first .. first + RET_BLOCK - 1 into registers
 #pragma unroll
         for (int j = 0; j < LOADS; ++j) {
-            const int e = tid + RET_THREADS * j, t = e / width, d = e % width;
+            const int e = tid + RET_THREADS * j, t = e / WIDTH, d = e % WIDTH;
             const bool ok = first + t < count && d < dim;
             q_next[j] = ok ? q_head[(int64_t)(first + t) * qk_stride + d] : 0.0f;
-            k_next[j] = ok ? k_head[(int64_t)(first + t) * qk_stride + d] : 0.0f;
+            if constexpr (!CORRECT) k_next[j] = ok ? k_head[(int64_t)(first + t) * qk_stride + d] : 0.0f;
         }
+        if constexpr (!CORRECT) {
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int e = tid + RET_THREADS * j, t = e / RET_COLS, cc = e % RET_COLS;
-            const bool ok = first + t < count && col0 + cc < vdim;
-            v_next[j] = ok ? to_float<T>(v_head[(int64_t)(first + t) * v_stride + cc]) : 0.0f;
+            for (int j = 0; j < V_LOADS; ++j) {
+                const int e = tid + RET_THREADS * j, t = e / COLS, cc = e % COLS;
+                const bool ok = e < RET_BLOCK * COLS && first + t < count && col0 + cc < vdim;
+                v_next[j] = ok ? to_float<T>(v_head[(int64_t)(first + t) * v_stride + cc]) : 0.0f;
+            }
         }
     };
     auto stage = [&]() {
 #pragma unroll
         for (int j = 0; j < LOADS; ++j) {
             const int e = tid + RET_THREADS * j;
-            q_s[e / width][e % width] = q_next[j];
-            k_s[e / width][e % width] = k_next[j];
+            q_s[e / WIDTH][e % WIDTH] = q_next[j];
+            if constexpr (!CORRECT) k_s[e / WIDTH][e % WIDTH] = k_next[j];
         }
+        if constexpr (!CORRECT) {
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int e = tid + RET_THREADS * j;
-            v_s[e / RET_COLS][e % RET_COLS] = v_next[j];
+            for (int j = 0; j < V_LOADS; ++j) {
+                const int e = tid + RET_THREADS * j;
+                if (e < RET_BLOCK * COLS) v_s[e / COLS][e % COLS] = v_next[j];
+            }
         }
     };
 
@@ -133,31 +168,90 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
     for (int first = 0; first < count; first += RET_BLOCK) {
         __syncthreads();                          // the block before is read
         stage();
+        if (CORRECT && tid < RET_BLOCK) power_s[tid] = powf(a, (float)(first + tid + 1));
         __syncthreads();
         if (first + RET_BLOCK < count) fetch(first + RET_BLOCK);
         const int here = min(RET_BLOCK, count - first);
-        for (int t = 0; t < here; ++t) {
-            const float vt = v_s[t][col];
-            float sum = 0.0f;
+        float sums[RET_BLOCK];
 #pragma unroll
-            for (int i = 0; i < ROWS; ++i) {
-                const int d = group + RET_GROUPS * i;
-                s[i] = __fmaf_rn(k_s[t][d], vt, __fmul_rn(a, s[i]));
-                sum = __fmaf_rn(s[i], q_s[t][d], sum);
+        for (int t = 0; t < RET_BLOCK; ++t) {
+            sums[t] = 0.0f;
+            if (t < here) {                       // the state moves in the order of the tokens, and only by real ones
+                float vt = 0.0f;
+                if constexpr (!CORRECT) vt = v_s[t][col];
+                float sum = 0.0f;
+#pragma unroll
+                for (int j = 0; j < ROWS / 4; ++j) {
+                    const float4 qq = *reinterpret_cast<const float4*>(&q_s[t][4 * (group + GROUPS * j)]);
+                    if constexpr (!CORRECT) {
+                        const float4 kk = *reinterpret_cast<const float4*>(&k_s[t][4 * (group + GROUPS * j)]);
+                        s[4 * j + 0] = __fmaf_rn(kk.x, vt, __fmul_rn(a, s[4 * j + 0]));
+                        s[4 * j + 1] = __fmaf_rn(kk.y, vt, __fmul_rn(a, s[4 * j + 1]));
+                        s[4 * j + 2] = __fmaf_rn(kk.z, vt, __fmul_rn(a, s[4 * j + 2]));
+                        s[4 * j + 3] = __fmaf_rn(kk.w, vt, __fmul_rn(a, s[4 * j + 3]));
+                    }
+                    sum = __fmaf_rn(s[4 * j + 0], qq.x, sum);
+                    sum = __fmaf_rn(s[4 * j + 1], qq.y, sum);
+                    sum = __fmaf_rn(s[4 * j + 2], qq.z, sum);
+                    sum = __fmaf_rn(s[4 * j + 3], qq.w, sum);
+                }
+                sums[t] = sum;
             }
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            if (live && group == 0)
-                out[(int64_t)(begin + first + t) * heads * vdim + (int64_t)head * vdim + c] = sum;
         }
+#pragma unroll
+        for (int lanes = 1; lanes < GROUPS; lanes <<= 1)      // the tokens' sums travel side by side
+#pragma unroll
+            for (int t = 0; t < RET_BLOCK; ++t) sums[t] += __shfl_xor_sync(0xffffffffu, sums[t], lanes);
+#pragma unroll
+        for (int t = 0; t < RET_BLOCK; ++t)
+            if (live && t < here && group == t % GROUPS) {
+                float* o = out + (int64_t)(begin + first + t) * heads * vdim + (int64_t)head * vdim + c;
+                *o = CORRECT ? __fmaf_rn(power_s[t], sums[t], *o) : sums[t];     // decay^(t + 1) S_0^T q_t
+            }
     }
-    if (live) {
+    if (live && !CORRECT) {
 #pragma unroll
         for (int i = 0; i < ROWS; ++i) {
-            const int d = group + RET_GROUPS * i;
+            const int d = 4 * (group + GROUPS * (i >> 2)) + (i & 3);
             if (d < dim) mine[(int64_t)d * vdim] = s[i];
         }
     }
+}
+
+// The states the pieces of an entry start from.  parts[piece] holds what the piece's tokens add to a state
+// of zero; with n the piece's tokens, S_next = decay^n S + parts[piece].  A thread walks one element of the
+// state through the entry's pieces, leaves in parts[piece] the state the piece starts from, and in the
+// request's slot the state after the entry's last token.
+__global__ void __launch_bounds__(256) retention_combine_kernel(
+    float* __restrict__ state, float* __restrict__ parts, const float* __restrict__ decay,
+    const int* __restrict__ row_starts, const int* __restrict__ state_slots, const int* __restrict__ token_row,
+    int segment, int heads, int per) {
+    const int row = blockIdx.z, head = blockIdx.y, e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= per) return;
+    int before = 0;
+    for (int r = 0; r < row; ++r) before += (row_starts[r + 1] - row_starts[r] + segment - 1) / segment;
+    const int begin = row_starts[row], tokens = row_starts[row + 1] - begin;
+    if (tokens <= 0 || token_row[begin] < 0) return;
+    const int pieces = (tokens + segment - 1) / segment;
+    const float a = decay[head];
+    const float whole = powf(a, (float)segment);
+    float* mine = state + ((int64_t)state_slots[row] * heads + head) * per + e;
+    float* first = parts + ((int64_t)before * heads + head) * per + e;
+    const int64_t apart = (int64_t)heads * per;
+    float s = *mine;
+    for (int j0 = 0; j0 < pieces; j0 += 8) {      // eight pieces' loads are in flight together
+        float added[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) added[u] = j0 + u < pieces ? first[(j0 + u) * apart] : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (j0 + u >= pieces) break;
+            first[(j0 + u) * apart] = s;
+            const int n = min(segment, tokens - (j0 + u) * segment);
+            s = __fmaf_rn(n == segment ? whole : powf(a, (float)n), s, added[u]);
+        }
+    }
+    *mine = s;
 }
 
 #define RET_ACT_NONE 0
@@ -203,42 +297,93 @@ extern "C" int tvb_retention_prepare(const void* proj, long long token_stride, i
                                                 rot_dims / 2 > RET_MAX_TURNED || pairing < 0 || pairing > 1)))
         return TVB_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
+    // few tokens: slices of a row's 2 * heads * dim elements go to CTAs of their own, up to eight elements a thread
+    const int slices = tokens >= 1024 ? 1 : max(1, min(64, (2 * heads * dim + 1023) / 1024));
+    const dim3 tokens_by_slices(tokens, slices);
     if (dtype == TVB_F32)
-        retention_prepare_kernel<float><<<tokens, 128, 0, s>>>((const float*)proj, token_stride, q_at, k_at, heads, dim,
+        retention_prepare_kernel<float><<<tokens_by_slices, 128, 0, s>>>((const float*)proj, token_stride, q_at, k_at, heads, dim,
                                                                inv_freq, rot_dims, pairing, key_scale, positions, q_out, k_out);
     else if (dtype == TVB_BF16)
-        retention_prepare_kernel<bf16><<<tokens, 128, 0, s>>>((const bf16*)proj, token_stride, q_at, k_at, heads, dim,
+        retention_prepare_kernel<bf16><<<tokens_by_slices, 128, 0, s>>>((const bf16*)proj, token_stride, q_at, k_at, heads, dim,
                                                               inv_freq, rot_dims, pairing, key_scale, positions, q_out, k_out);
     else return TVB_BAD_ARGUMENT;
     return tvb_last_error();
 }
 
-extern "C" int tvb_retention_max_dim() { return RET_GROUPS * 64; }
+extern "C" int tvb_retention_max_dim() { return 256; }
+
+static int retention_sm_count() {
+    static int sms = 0;
+    if (sms <= 0) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    return sms;
+}
 
 // q, k: float32 [tokens, heads * dim]; v: [tokens, >= heads * vdim] of the storage type with rows
 // `v_stride` elements apart; state: float32 [slots, heads, dim, vdim]; decay: float32 [heads];
 // row_starts [rows + 1], state_slots [rows], token_row [tokens] (negative: padding); out: float32
-// [tokens, heads * vdim].
+// [tokens, heads * vdim].  `lanes` (0: chosen here) is the number of lanes that share a column of the
+// state: 4, 8, 16 or 32, each with at least one float4 of the key.
+//
+// segment == 0: a CTA walks a whole entry, from the request's state to the state it leaves.
+// segment > 0: every entry is cut into pieces of `segment` tokens that run side by side (three launches):
+// each piece from a state of zero, which leaves o without what came before the piece and, in
+// parts [pieces, heads, dim, vdim], what the piece adds; then the states the pieces start from, along every
+// entry; then decay^(t + 1) S_start^T q_t added to the piece's token t.  `pieces` is at least the number of
+// pieces of all entries (tokens / segment + rows always is).
 extern "C" int tvb_retention_scan(const float* q, const float* k, const void* v, long long v_stride, float* state,
                                   const float* decay, const int* row_starts, const int* state_slots,
                                   const int* token_row, float* out, int rows, int heads, int dim, int vdim,
-                                  int dtype, void* stream) {
+                                  int lanes, float* parts, int segment, int pieces, int dtype, void* stream) {
     if (rows <= 0) return 0;
-    if (heads <= 0 || heads > 65535 || dim <= 0 || dim > RET_GROUPS * 64 || vdim <= 0) return TVB_BAD_ARGUMENT;
-    const dim3 grid(rows, heads, (vdim + RET_COLS - 1) / RET_COLS);
+    if (heads <= 0 || heads > 65535 || dim <= 0 || dim > 256 || vdim <= 0 || rows > 65535 || segment < 0 ||
+        (segment > 0 && (!parts || pieces <= 0)))
+        return TVB_BAD_ARGUMENT;
+    const int blocks = segment > 0 ? pieces : rows;
+    const int quads = (dim + 3) / 4;
+    int most = 4;                                 // the most lanes a column that all hold part of the key
+    while (most < 32 && most * 2 <= quads) most *= 2;
+    if (lanes == 0) {                             // the fewest lanes that give every SM two CTAs
+        const long long wanted = 2LL * retention_sm_count();
+        for (lanes = 4; lanes < most; lanes *= 2)
+            if ((long long)blocks * heads * ((vdim + RET_THREADS / lanes - 1) / (RET_THREADS / lanes)) >= wanted) break;
+    }
+    if ((lanes != 4 && lanes != 8 && lanes != 16 && lanes != 32) || lanes > most) return TVB_BAD_ARGUMENT;
+    const int cols = RET_THREADS / lanes;
+    const dim3 grid(blocks, heads, (vdim + cols - 1) / cols);
     if (grid.z > 65535) return TVB_BAD_ARGUMENT;
+    const int need = (dim + lanes - 1) / lanes;   // rows of the state a thread
     cudaStream_t s = (cudaStream_t)stream;
-#define GO(T, ROWS) retention_scan_kernel<T, ROWS><<<grid, RET_THREADS, 0, s>>>(                                   \
-        q, k, (const T*)v, v_stride, state, decay, row_starts, state_slots, token_row, out, heads, dim, vdim)
-#define BY_DIM(T)                                                                                                  \
-    if (dim <= RET_GROUPS * 8) GO(T, 8);                                                                           \
-    else if (dim <= RET_GROUPS * 16) GO(T, 16);                                                                    \
-    else if (dim <= RET_GROUPS * 32) GO(T, 32);                                                                    \
-    else GO(T, 64)
-    if (dtype == TVB_F32) { BY_DIM(float); }
-    else if (dtype == TVB_BF16) { BY_DIM(bf16); }
+#define GO(T, G, R, C) retention_scan_kernel<T, G, R, C><<<grid, RET_THREADS, 0, s>>>(                              \
+        q, k, (const T*)v, v_stride, state, decay, row_starts, state_slots, token_row, out, parts, segment, rows,  \
+        heads, dim, vdim)
+#define BY_ROWS(T, G, C)                                                                                           \
+    if (need <= 4) GO(T, G, 4, C);                                                                                 \
+    else if (need <= 8) GO(T, G, 8, C);                                                                            \
+    else if (G <= 16 && need <= 16) GO(T, (G <= 16 ? G : 16), 16, C);                                              \
+    else if (G <= 8 && need <= 32) GO(T, (G <= 8 ? G : 8), 32, C);                                                 \
+    else if (G <= 4 && need <= 64) GO(T, (G <= 4 ? G : 4), 64, C);                                                 \
+    else return TVB_BAD_ARGUMENT
+#define BY_LANES(T, C)                                                                                             \
+    if (lanes == 4) { BY_ROWS(T, 4, C); }                                                                          \
+    else if (lanes == 8) { BY_ROWS(T, 8, C); }                                                                     \
+    else if (lanes == 16) { BY_ROWS(T, 16, C); }                                                                   \
+    else { BY_ROWS(T, 32, C); }
+    if (dtype == TVB_F32) { BY_LANES(float, false) }
+    else if (dtype == TVB_BF16) { BY_LANES(bf16, false) }
     else return TVB_BAD_ARGUMENT;
-#undef BY_DIM
+    if (segment > 0) {
+        const int per = dim * vdim;
+        retention_combine_kernel<<<dim3((per + 255) / 256, heads, rows), 256, 0, s>>>(
+            state, parts, decay, row_starts, state_slots, token_row, segment, heads, per);
+        BY_LANES(float, true)                     // the correcting pass reads no values: one type will do
+    }
+#undef BY_LANES
+#undef BY_ROWS
 #undef GO
     return tvb_last_error();
 }

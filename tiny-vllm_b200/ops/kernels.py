@@ -748,6 +748,21 @@ def route_gated_act(logits: torch.Tensor, proj: torch.Tensor, *, experts: int, t
 # --------------------------------------------------- retention: linear attention with a decay a head
 RETENTION_MAX_DIM = 256
 RETENTION_ACTS = {None: 0, "silu": 1, "sigmoid": 2}
+SM_COUNT = 148                    # a B200's SMs: what the choice of a piece's size fills
+
+
+def retention_segment(tokens: int, rows: int, heads: int, vdim: int) -> int:
+    """Tokens a piece of the scan.  0 (whole entries) where the entries' (head, 32 columns) CTAs already give
+    every other SM one: the scan is bound by shared-memory reads an SM, not by waiting, and pieces add the
+    correcting pass (measured: 16 heads of 128 gain a third, 32 heads lose a sixth).  Else, for prompts, the
+    longest of 256, 128 and 64 tokens that gives the SMs four CTAs each."""
+    per_piece = heads * -(-vdim // 32)
+    if 2 * rows * per_piece >= SM_COUNT or tokens < 4 * max(rows, 1) or tokens < 256:
+        return 0
+    segment = 256
+    while segment > 64 and (tokens // segment) * per_piece < 4 * SM_COUNT:
+        segment //= 2
+    return segment
 
 
 def retention(proj: torch.Tensor, *, q_at: int, k_at: int, v_at: int, g_at: int | None, heads: int, dim: int,
@@ -755,7 +770,8 @@ def retention(proj: torch.Tensor, *, q_at: int, k_at: int, v_at: int, g_at: int 
               state_slots: torch.Tensor, token_row: torch.Tensor, positions: torch.Tensor,
               inv_freq: torch.Tensor | None = None, rot_dims: int = 0, pairing: str = "half_split",
               key_scale: float = 1.0, unit_norm: bool = True, eps: float = 0.0, gate_act: str | None = "silu",
-              out: torch.Tensor | None = None, raw_out: torch.Tensor | None = None) -> torch.Tensor:
+              out: torch.Tensor | None = None, raw_out: torch.Tensor | None = None, lanes: int = 0,
+              segment: int | None = None) -> torch.Tensor:
     """Retention between a mixer's packed input projection and its output projection.
 
     ``proj`` [tokens, columns] holds q heads (``dim`` wide) from column ``q_at``, k heads from ``k_at``,
@@ -766,7 +782,14 @@ def retention(proj: torch.Tensor, *, q_at: int, k_at: int, v_at: int, g_at: int 
     position * ``inv_freq`` on their first ``rot_dims`` dimensions and k is multiplied by ``key_scale``,
     all in float32.  Every head's o is divided by its root mean square (``unit_norm``, with ``eps``),
     multiplied by act(gate) and rounded to the projection's type: [tokens, heads * vdim].  ``raw_out``
-    (float32 [tokens, heads * vdim]) receives o itself."""
+    (float32 [tokens, heads * vdim]) receives o itself.  ``lanes`` (4, 8, 16 or 32, at most a quarter of
+    ``dim``; 0: as many as give every SM work) is the number of lanes that share a column of the state.
+
+    ``segment``: 0 walks every entry token by token in one CTA a (head, block of columns); n > 0 cuts the
+    entries into pieces of n tokens that run side by side from a state of zero, joins the pieces' states
+    along each entry and adds to every token what the state before its piece gives it (S_0 reaches token t
+    of a piece as decay^(t + 1) S_0^T q_t).  None chooses: whole entries for steps of few tokens, pieces of
+    64 to 256 tokens, enough of them to fill the SMs, for prompts."""
     _need_cuda(proj, decay, state, row_starts, state_slots, token_row, positions, inv_freq, out, raw_out)
     tokens = proj.shape[0]
     rows = state_slots.shape[0]
@@ -800,6 +823,12 @@ def retention(proj: torch.Tensor, *, q_at: int, k_at: int, v_at: int, g_at: int 
     elif raw_out.shape != (tokens, heads * vdim) or raw_out.dtype != torch.float32 or not raw_out.is_contiguous():
         raise KernelError("retention: raw_out must be contiguous float32 [tokens, heads * vdim]")
     turned = torch.empty((2, tokens, heads * dim), dtype=torch.float32, device=proj.device)
+    if segment is None:
+        segment = retention_segment(tokens, rows, heads, vdim)
+    if segment < 0:
+        raise KernelError("retention: a piece has at least one token")
+    pieces = tokens // segment + rows if segment else 0
+    parts = torch.empty((pieces, heads, dim, vdim), dtype=torch.float32, device=proj.device) if segment else None
     tag = dtype_tag(proj.dtype)
     prepare = _fn("retention", "tvb_retention_prepare",
                   [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p,
@@ -809,10 +838,11 @@ def retention(proj: torch.Tensor, *, q_at: int, k_at: int, v_at: int, g_at: int 
                    tokens, tag, _stream()), "retention_prepare")
     scan = _fn("retention", "tvb_retention_scan",
                [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                c_int, c_int, c_int, c_int, c_int, c_void_p])
+                c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
     _check(scan(turned[0].data_ptr(), turned[1].data_ptr(), proj.data_ptr() + v_at * proj.element_size(),
                 proj.stride(0), state.data_ptr(), decay.data_ptr(), row_starts.data_ptr(), state_slots.data_ptr(),
-                token_row.data_ptr(), raw_out.data_ptr(), rows, heads, dim, vdim, tag, _stream()), "retention_scan")
+                token_row.data_ptr(), raw_out.data_ptr(), rows, heads, dim, vdim, lanes, _ptr(parts), segment, pieces, tag,
+                _stream()), "retention_scan", launches=3 if segment else 1)
     finish = _fn("retention", "tvb_retention_finish",
                  [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_float, c_int,
                   c_int, c_void_p])
