@@ -104,11 +104,11 @@ def test_retention_from_a_carried_state(heads, dim, vdim, rot, gate, dtype):
     for length in lengths:
         row_starts.append(row_starts[-1] + length)
     inv_freq = torch.tensor([base ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=F64).float().to(CUDA) if rot else None
-    # every number of lanes a column of the state that the key size takes, and the kernel's own choice (0)
+    # every number of lanes a tile of columns of the state that the key size takes, and the kernel's own choice (0)
     # ... as whole entries (0), in pieces of 5, 64 and 403 tokens (the long entry is one piece, 81 or 7, the
     # single tokens a piece each), and as the wrapper chooses for a step of this size
-    ways = [(lanes, 0) for lanes in [0] + [n for n in (4, 8, 16, 32) if n == 4 or n <= -(-dim // 4)]]
-    ways += [(0, 5), (4, 64), (0, 403), (0, None)]
+    ways = [(lanes, 0) for lanes in [0] + [n for n in (4, 8, 16, 32) if n * 8 >= dim]]
+    ways += [(0, 5), (32, 64), (0, 403), (0, None)]
     for lanes, segment in ways:
         device_state = state.to(CUDA)
         raw = torch.empty(tokens, heads * vdim, dtype=torch.float32, device=CUDA)
@@ -131,7 +131,7 @@ def test_retention_from_a_carried_state(heads, dim, vdim, rot, gate, dtype):
             assert (o @ v2) / (o.norm() * v2.norm()) > 0.8
         untouched = [s for s in range(6) if s not in slots]
         assert torch.equal(device_state[untouched].cpu(), state[untouched])
-    with pytest.raises(kernels.KernelError):      # more lanes than the key has float4s
+    with pytest.raises(kernels.KernelError):      # no such number of lanes
         kernels.retention(
             proj.to(dtype).to(CUDA), q_at=q_at, k_at=k_at, v_at=v_at, g_at=None, heads=heads, dim=dim, vdim=vdim,
             decay=torch.tensor(decay, dtype=torch.float32, device=CUDA), state=state.to(CUDA),

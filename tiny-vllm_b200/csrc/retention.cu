@@ -10,8 +10,10 @@
 //                       or (2i, 2i + 1)), k then multiplied by `key_scale`
 //   retention_scan      the recurrence itself, token by token from the state the request's earlier
 //                       tokens left (a slot of the state arena) to the state its next tokens start
-//                       from; a CTA has one (request, head, 128 / lanes value columns), a thread one
-//                       of `lanes` parts of a column of the state in registers; tokens come in blocks of eight through
+//                       from (or, for long prompts, in pieces side by side that a second kernel joins and
+//                       a third corrects); a CTA has one (request or piece, head, block of value columns),
+//                       a thread up to eight rows by eight columns of the state in registers; tokens come
+//                       in blocks of four through
 //                       shared memory, the next block's loads in flight while this one is computed
 //   retention_finish    every head's o divided by its root mean square (or not), times act(gate),
 //                       rounded once to the storage type
@@ -59,30 +61,35 @@ __global__ void __launch_bounds__(128) retention_prepare_kernel(
 }
 
 #define RET_THREADS 128
-#define RET_BLOCK 8                               // tokens that wait in shared memory
+#define RET_BLOCK 4                               // tokens that wait in shared memory
+#define RET_TILE 8                                // value columns a thread
+#define RET_SUMS (RET_BLOCK * RET_TILE)           // sums a thread holds after a block of tokens
 
-// GROUPS: lanes that share a column of the state (a power of two up to 32); a CTA has
-// RET_THREADS / GROUPS value columns.  ROWS: rows of the state a thread holds, a multiple of four
-// (dim <= GROUPS * ROWS): rows 4 (group + GROUPS j) .. + 3 for j = 0 .. ROWS / 4 - 1, so that the lanes of
-// a column read neighbouring float4s of a token's q and k.  The host takes more lanes a column where
-// few (request, head) pairs would leave SMs idle: a long prompt alone runs on GROUPS = 16 or 32.
+// A thread holds ROWS rows by RET_TILE columns of the state: rows 4 (group + GROUPS j) .. + 3 for
+// j = 0 .. ROWS / 4 - 1 (dim <= GROUPS * ROWS), so that the GROUPS lanes of a tile of columns read
+// neighbouring float4s of a token's q and k; a CTA has RET_THREADS / GROUPS tiles of columns.  A token costs a
+// thread ROWS / 2 + 2 float4s from shared memory for 3 * ROWS * RET_TILE multiply-adds, which keeps the
+// arithmetic, not the shared memory, the busier of the two.  The lanes' partial sums of a block of tokens are
+// added by halving: at every step a lane hands half of its sums to the lane one bit away and keeps the
+// other half, so that after log2(GROUPS) steps lane g holds sums g * RET_SUMS / GROUPS and on, complete.
 template <typename T, int GROUPS, int ROWS, bool CORRECT>
 __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const T* __restrict__ v, int64_t v_stride,
     float* __restrict__ state, const float* __restrict__ decay, const int* __restrict__ row_starts,
     const int* __restrict__ state_slots, const int* __restrict__ token_row, float* __restrict__ out,
     float* __restrict__ parts, int segment, int rows, int heads, int dim, int vdim) {
-    constexpr int COLS = RET_THREADS / GROUPS;
+    constexpr int COLS = RET_THREADS / GROUPS * RET_TILE;                   // value columns a CTA
     constexpr int WIDTH = GROUPS * ROWS;
-    constexpr int LOADS = RET_BLOCK * WIDTH / RET_THREADS;                  // q (and k) values a thread fetches a block
-    constexpr int V_LOADS = (RET_BLOCK * COLS + RET_THREADS - 1) / RET_THREADS;
-    static_assert(ROWS % 4 == 0 && LOADS >= 1 && RET_BLOCK * WIDTH % RET_THREADS == 0, "retention_scan: tile");
+    constexpr int LOADS = (RET_BLOCK * WIDTH + RET_THREADS - 1) / RET_THREADS;  // q (and k) values a thread fetches a block
+    constexpr int V_LOADS = RET_BLOCK * COLS / RET_THREADS;
+    constexpr int LEFT = RET_SUMS / GROUPS;                                 // sums a lane ends with
+    static_assert(ROWS % 4 == 0 && RET_SUMS % GROUPS == 0 && RET_BLOCK * COLS % RET_THREADS == 0, "retention_scan: tile");
     __shared__ __align__(16) float q_s[RET_BLOCK][WIDTH];
     __shared__ __align__(16) float k_s[CORRECT ? 1 : RET_BLOCK][CORRECT ? 4 : WIDTH];
-    __shared__ float v_s[CORRECT ? 1 : RET_BLOCK][COLS];
-    __shared__ float power_s[RET_BLOCK];
+    __shared__ __align__(16) float v_s[CORRECT ? 1 : RET_BLOCK][CORRECT ? 4 : COLS];
+    __shared__ float power_s[2][RET_BLOCK];    // decay^(t + 1) of this block's tokens and of the next's
     const int head = blockIdx.y, col0 = blockIdx.z * COLS;
-    const int tid = threadIdx.x, group = tid % GROUPS, col = tid / GROUPS;
+    const int tid = threadIdx.x, group = tid % GROUPS, tile = tid / GROUPS;
     // whole entries (segment == 0: block x is the entry) or pieces of `segment` tokens (block x is the
     // piece, counted through the entries in order)
     int row = blockIdx.x, begin, count;
@@ -103,11 +110,13 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
         count = min(segment, tokens - piece * segment);
     }
     if (count <= 0) return;
-    const int c = col0 + col;
-    const bool live = c < vdim;
+    const int c = col0 + tile * RET_TILE;         // the thread's first column
+    const int64_t out_stride = (int64_t)heads * vdim;
     if (token_row[begin] < 0) {                   // a padding row of a recorded batch: no request, no state
-        if (!CORRECT && live && group == 0)
-            for (int t = 0; t < count; ++t) out[(int64_t)(begin + t) * heads * vdim + (int64_t)head * vdim + c] = 0.0f;
+        if (!CORRECT && group == 0)
+            for (int t = 0; t < count; ++t)
+                for (int cc = 0; cc < RET_TILE; ++cc)
+                    if (c + cc < vdim) out[(int64_t)(begin + t) * out_stride + (int64_t)head * vdim + c + cc] = 0.0f;
         return;
     }
     const float a = decay[head];
@@ -116,13 +125,32 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
     // correcting pass reads that and adds what it gives to every token of the piece
     float* mine = (segment <= 0 ? state + (((int64_t)state_slots[row] * heads + head) * dim) * vdim
                                 : parts + (((int64_t)blockIdx.x * heads + head) * dim) * vdim) + c;
-    float s[ROWS];
+    // then a float4 of a row of the state is whole and aligned
+    const bool by_four = (vdim & 3) == 0 && ((reinterpret_cast<uintptr_t>(state) | reinterpret_cast<uintptr_t>(parts)) & 15) == 0;
+    float s[ROWS][RET_TILE];
     bool any = false;
 #pragma unroll
     for (int i = 0; i < ROWS; ++i) {
         const int d = 4 * (group + GROUPS * (i >> 2)) + (i & 3);
-        s[i] = (live && d < dim && (segment <= 0 || CORRECT)) ? mine[(int64_t)d * vdim] : 0.0f;
-        any = any || s[i] != 0.0f;
+#pragma unroll
+        for (int cc = 0; cc < RET_TILE; ++cc) s[i][cc] = 0.0f;
+        if (d < dim && (segment <= 0 || CORRECT)) {
+            const float* from = mine + (int64_t)d * vdim;
+            if (by_four) {
+#pragma unroll
+                for (int h = 0; h < RET_TILE / 4; ++h)
+                    if (c + 4 * h < vdim) {
+                        const float4 x = *reinterpret_cast<const float4*>(from + 4 * h);
+                        s[i][4 * h] = x.x; s[i][4 * h + 1] = x.y; s[i][4 * h + 2] = x.z; s[i][4 * h + 3] = x.w;
+                    }
+            } else {
+#pragma unroll
+                for (int cc = 0; cc < RET_TILE; ++cc)
+                    if (c + cc < vdim) s[i][cc] = from[cc];
+            }
+#pragma unroll
+            for (int cc = 0; cc < RET_TILE; ++cc) any = any || s[i][cc] != 0.0f;
+        }
     }
     if (CORRECT && !__syncthreads_or(any)) return;            // the request's first piece: nothing came before
     const int64_t qk_stride = (int64_t)heads * dim;
@@ -135,7 +163,7 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
 #pragma unroll
         for (int j = 0; j < LOADS; ++j) {
             const int e = tid + RET_THREADS * j, t = e / WIDTH, d = e % WIDTH;
-            const bool ok = first + t < count && d < dim;
+            const bool ok = e < RET_BLOCK * WIDTH && first + t < count && d < dim;
             q_next[j] = ok ? q_head[(int64_t)(first + t) * qk_stride + d] : 0.0f;
             if constexpr (!CORRECT) k_next[j] = ok ? k_head[(int64_t)(first + t) * qk_stride + d] : 0.0f;
         }
@@ -143,7 +171,7 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
 #pragma unroll
             for (int j = 0; j < V_LOADS; ++j) {
                 const int e = tid + RET_THREADS * j, t = e / COLS, cc = e % COLS;
-                const bool ok = e < RET_BLOCK * COLS && first + t < count && col0 + cc < vdim;
+                const bool ok = first + t < count && col0 + cc < vdim;
                 v_next[j] = ok ? to_float<T>(v_head[(int64_t)(first + t) * v_stride + cc]) : 0.0f;
             }
         }
@@ -152,68 +180,103 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
 #pragma unroll
         for (int j = 0; j < LOADS; ++j) {
             const int e = tid + RET_THREADS * j;
-            q_s[e / WIDTH][e % WIDTH] = q_next[j];
-            if constexpr (!CORRECT) k_s[e / WIDTH][e % WIDTH] = k_next[j];
+            if (e < RET_BLOCK * WIDTH) {
+                q_s[e / WIDTH][e % WIDTH] = q_next[j];
+                if constexpr (!CORRECT) k_s[e / WIDTH][e % WIDTH] = k_next[j];
+            }
         }
         if constexpr (!CORRECT) {
 #pragma unroll
             for (int j = 0; j < V_LOADS; ++j) {
                 const int e = tid + RET_THREADS * j;
-                if (e < RET_BLOCK * COLS) v_s[e / COLS][e % COLS] = v_next[j];
+                v_s[e / COLS][e % COLS] = v_next[j];
             }
         }
     };
 
     fetch(0);
+    if (CORRECT && tid < RET_BLOCK) power_s[0][tid] = powf(a, (float)(tid + 1));
     for (int first = 0; first < count; first += RET_BLOCK) {
+        const int turn = (first / RET_BLOCK) & 1;
         __syncthreads();                          // the block before is read
         stage();
-        if (CORRECT && tid < RET_BLOCK) power_s[tid] = powf(a, (float)(first + tid + 1));
         __syncthreads();
         if (first + RET_BLOCK < count) fetch(first + RET_BLOCK);
+        if (CORRECT && tid < RET_BLOCK) power_s[turn ^ 1][tid] = powf(a, (float)(first + RET_BLOCK + tid + 1));
         const int here = min(RET_BLOCK, count - first);
-        float sums[RET_BLOCK];
+        float sums[RET_SUMS];
 #pragma unroll
         for (int t = 0; t < RET_BLOCK; ++t) {
-            sums[t] = 0.0f;
+#pragma unroll
+            for (int cc = 0; cc < RET_TILE; ++cc) sums[t * RET_TILE + cc] = 0.0f;
             if (t < here) {                       // the state moves in the order of the tokens, and only by real ones
-                float vt = 0.0f;
-                if constexpr (!CORRECT) vt = v_s[t][col];
-                float sum = 0.0f;
+                float vv[RET_TILE];
+                if constexpr (!CORRECT) {
+#pragma unroll
+                    for (int h = 0; h < RET_TILE / 4; ++h) {
+                        const float4 x = *reinterpret_cast<const float4*>(&v_s[t][tile * RET_TILE + 4 * h]);
+                        vv[4 * h] = x.x; vv[4 * h + 1] = x.y; vv[4 * h + 2] = x.z; vv[4 * h + 3] = x.w;
+                    }
+                }
 #pragma unroll
                 for (int j = 0; j < ROWS / 4; ++j) {
                     const float4 qq = *reinterpret_cast<const float4*>(&q_s[t][4 * (group + GROUPS * j)]);
+                    const float qr[4] = {qq.x, qq.y, qq.z, qq.w};
                     if constexpr (!CORRECT) {
                         const float4 kk = *reinterpret_cast<const float4*>(&k_s[t][4 * (group + GROUPS * j)]);
-                        s[4 * j + 0] = __fmaf_rn(kk.x, vt, __fmul_rn(a, s[4 * j + 0]));
-                        s[4 * j + 1] = __fmaf_rn(kk.y, vt, __fmul_rn(a, s[4 * j + 1]));
-                        s[4 * j + 2] = __fmaf_rn(kk.z, vt, __fmul_rn(a, s[4 * j + 2]));
-                        s[4 * j + 3] = __fmaf_rn(kk.w, vt, __fmul_rn(a, s[4 * j + 3]));
+                        const float kr[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+#pragma unroll
+                            for (int cc = 0; cc < RET_TILE; ++cc)
+                                s[4 * j + i][cc] = __fmaf_rn(kr[i], vv[cc], __fmul_rn(a, s[4 * j + i][cc]));
                     }
-                    sum = __fmaf_rn(s[4 * j + 0], qq.x, sum);
-                    sum = __fmaf_rn(s[4 * j + 1], qq.y, sum);
-                    sum = __fmaf_rn(s[4 * j + 2], qq.z, sum);
-                    sum = __fmaf_rn(s[4 * j + 3], qq.w, sum);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+#pragma unroll
+                        for (int cc = 0; cc < RET_TILE; ++cc)
+                            sums[t * RET_TILE + cc] = __fmaf_rn(s[4 * j + i][cc], qr[i], sums[t * RET_TILE + cc]);
                 }
-                sums[t] = sum;
+            }
+        }
+        // halving: with n sums left, the lanes whose bit is set keep the upper n / 2 and hand over the lower
+#pragma unroll
+        for (int bit = GROUPS / 2, n = RET_SUMS; bit >= 1; bit >>= 1, n >>= 1) {
+            const bool upper = (group & bit) != 0;
+#pragma unroll
+            for (int i = 0; i < n / 2; ++i) {
+                const float hand = upper ? sums[i] : sums[i + n / 2];
+                const float keep = upper ? sums[i + n / 2] : sums[i];
+                sums[i] = keep + __shfl_xor_sync(0xffffffffu, hand, bit);
             }
         }
 #pragma unroll
-        for (int lanes = 1; lanes < GROUPS; lanes <<= 1)      // the tokens' sums travel side by side
-#pragma unroll
-            for (int t = 0; t < RET_BLOCK; ++t) sums[t] += __shfl_xor_sync(0xffffffffu, sums[t], lanes);
-#pragma unroll
-        for (int t = 0; t < RET_BLOCK; ++t)
-            if (live && t < here && group == t % GROUPS) {
-                float* o = out + (int64_t)(begin + first + t) * heads * vdim + (int64_t)head * vdim + c;
-                *o = CORRECT ? __fmaf_rn(power_s[t], sums[t], *o) : sums[t];     // decay^(t + 1) S_0^T q_t
+        for (int i = 0; i < LEFT; ++i) {          // sum group * LEFT + i is token (index / RET_TILE), column (index % RET_TILE)
+            const int index = group * LEFT + i, t = index / RET_TILE, cc = index % RET_TILE;
+            if (t < here && c + cc < vdim) {
+                float* o = out + (int64_t)(begin + first + t) * out_stride + (int64_t)head * vdim + c + cc;
+                *o = CORRECT ? __fmaf_rn(power_s[turn][t], sums[i], *o) : sums[i];     // decay^(t + 1) S_0^T q_t
             }
+        }
     }
-    if (live && !CORRECT) {
+    if constexpr (!CORRECT) {
 #pragma unroll
         for (int i = 0; i < ROWS; ++i) {
             const int d = 4 * (group + GROUPS * (i >> 2)) + (i & 3);
-            if (d < dim) mine[(int64_t)d * vdim] = s[i];
+            if (d < dim) {
+                float* to = mine + (int64_t)d * vdim;
+                if (by_four) {
+#pragma unroll
+                    for (int h = 0; h < RET_TILE / 4; ++h)
+                        if (c + 4 * h < vdim)
+                            *reinterpret_cast<float4*>(to + 4 * h) =
+                                make_float4(s[i][4 * h], s[i][4 * h + 1], s[i][4 * h + 2], s[i][4 * h + 3]);
+                } else {
+#pragma unroll
+                    for (int cc = 0; cc < RET_TILE; ++cc)
+                        if (c + cc < vdim) to[cc] = s[i][cc];
+                }
+            }
         }
     }
 }
@@ -222,11 +285,12 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
 // of zero; with n the piece's tokens, S_next = decay^n S + parts[piece].  A thread walks one element of the
 // state through the entry's pieces, leaves in parts[piece] the state the piece starts from, and in the
 // request's slot the state after the entry's last token.
+template <int VEC>                                // elements a thread: 4 (float4s, where rows of 4 fit) or 1
 __global__ void __launch_bounds__(256) retention_combine_kernel(
     float* __restrict__ state, float* __restrict__ parts, const float* __restrict__ decay,
     const int* __restrict__ row_starts, const int* __restrict__ state_slots, const int* __restrict__ token_row,
     int segment, int heads, int per) {
-    const int row = blockIdx.z, head = blockIdx.y, e = blockIdx.x * blockDim.x + threadIdx.x;
+    const int row = blockIdx.z, head = blockIdx.y, e = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (e >= per) return;
     int before = 0;
     for (int r = 0; r < row; ++r) before += (row_starts[r + 1] - row_starts[r] + segment - 1) / segment;
@@ -235,23 +299,35 @@ __global__ void __launch_bounds__(256) retention_combine_kernel(
     const int pieces = (tokens + segment - 1) / segment;
     const float a = decay[head];
     const float whole = powf(a, (float)segment);
+    const float rest = powf(a, (float)(tokens - (pieces - 1) * segment));      // the last piece may be shorter
     float* mine = state + ((int64_t)state_slots[row] * heads + head) * per + e;
     float* first = parts + ((int64_t)before * heads + head) * per + e;
     const int64_t apart = (int64_t)heads * per;
-    float s = *mine;
+    float s[VEC];
+    auto load = [&](const float* p, float* x) {
+        if constexpr (VEC == 4) { const float4 y = *reinterpret_cast<const float4*>(p); x[0] = y.x; x[1] = y.y; x[2] = y.z; x[3] = y.w; }
+        else x[0] = *p;
+    };
+    auto store = [&](float* p, const float* x) {
+        if constexpr (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+        else *p = x[0];
+    };
+    load(mine, s);
     for (int j0 = 0; j0 < pieces; j0 += 8) {      // eight pieces' loads are in flight together
-        float added[8];
+        float added[8][VEC];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) added[u] = j0 + u < pieces ? first[(j0 + u) * apart] : 0.0f;
+        for (int u = 0; u < 8; ++u)
+            if (j0 + u < pieces) load(first + (j0 + u) * apart, added[u]);
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             if (j0 + u >= pieces) break;
-            first[(j0 + u) * apart] = s;
-            const int n = min(segment, tokens - (j0 + u) * segment);
-            s = __fmaf_rn(n == segment ? whole : powf(a, (float)n), s, added[u]);
+            store(first + (j0 + u) * apart, s);
+            const float power = j0 + u == pieces - 1 ? rest : whole;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) s[i] = __fmaf_rn(power, s[i], added[u][i]);
         }
     }
-    *mine = s;
+    store(mine, s);
 }
 
 #define RET_ACT_NONE 0
@@ -312,22 +388,11 @@ extern "C" int tvb_retention_prepare(const void* proj, long long token_stride, i
 
 extern "C" int tvb_retention_max_dim() { return 256; }
 
-static int retention_sm_count() {
-    static int sms = 0;
-    if (sms <= 0) {
-        int device = 0;
-        if (cudaGetDevice(&device) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
-            sms = 148;
-    }
-    return sms;
-}
-
 // q, k: float32 [tokens, heads * dim]; v: [tokens, >= heads * vdim] of the storage type with rows
 // `v_stride` elements apart; state: float32 [slots, heads, dim, vdim]; decay: float32 [heads];
 // row_starts [rows + 1], state_slots [rows], token_row [tokens] (negative: padding); out: float32
-// [tokens, heads * vdim].  `lanes` (0: chosen here) is the number of lanes that share a column of the
-// state: 4, 8, 16 or 32, each with at least one float4 of the key.
+// [tokens, heads * vdim].  `lanes` (0: the fewest, or more where a B200's 148 SMs would idle) is the number of lanes that share a tile of eight columns
+// of the state: 4, 8, 16 or 32, with at most eight rows of the key a lane (lanes * 8 >= dim).
 //
 // segment == 0: a CTA walks a whole entry, from the request's state to the state it leaves.
 // segment > 0: every entry is cut into pieces of `segment` tokens that run side by side (three launches):
@@ -344,30 +409,24 @@ extern "C" int tvb_retention_scan(const float* q, const float* k, const void* v,
         (segment > 0 && (!parts || pieces <= 0)))
         return TVB_BAD_ARGUMENT;
     const int blocks = segment > 0 ? pieces : rows;
-    const int quads = (dim + 3) / 4;
-    int most = 4;                                 // the most lanes a column that all hold part of the key
-    while (most < 32 && most * 2 <= quads) most *= 2;
-    if (lanes == 0) {                             // the fewest lanes that give every SM two CTAs
-        const long long wanted = 2LL * retention_sm_count();
-        for (lanes = 4; lanes < most; lanes *= 2)
-            if ((long long)blocks * heads * ((vdim + RET_THREADS / lanes - 1) / (RET_THREADS / lanes)) >= wanted) break;
+    if (lanes == 0) {                             // the fewest that hold the key, more while SMs would idle
+        for (lanes = 4; lanes < 32 && lanes * 8 < dim; lanes *= 2) {}
+        while (lanes < 32 && (long long)blocks * heads * ((vdim + RET_THREADS / lanes * RET_TILE - 1) /
+                                                          (RET_THREADS / lanes * RET_TILE)) < 2 * 148)
+            lanes *= 2;
     }
-    if ((lanes != 4 && lanes != 8 && lanes != 16 && lanes != 32) || lanes > most) return TVB_BAD_ARGUMENT;
-    const int cols = RET_THREADS / lanes;
+    if ((lanes != 4 && lanes != 8 && lanes != 16 && lanes != 32) || lanes * 8 < dim) return TVB_BAD_ARGUMENT;
+    const int cols = RET_THREADS / lanes * RET_TILE;
     const dim3 grid(blocks, heads, (vdim + cols - 1) / cols);
     if (grid.z > 65535) return TVB_BAD_ARGUMENT;
-    const int need = (dim + lanes - 1) / lanes;   // rows of the state a thread
+    const bool few = (dim + lanes - 1) / lanes <= 4;          // rows of the state a lane: four or eight
     cudaStream_t s = (cudaStream_t)stream;
 #define GO(T, G, R, C) retention_scan_kernel<T, G, R, C><<<grid, RET_THREADS, 0, s>>>(                              \
         q, k, (const T*)v, v_stride, state, decay, row_starts, state_slots, token_row, out, parts, segment, rows,  \
         heads, dim, vdim)
 #define BY_ROWS(T, G, C)                                                                                           \
-    if (need <= 4) GO(T, G, 4, C);                                                                                 \
-    else if (need <= 8) GO(T, G, 8, C);                                                                            \
-    else if (G <= 16 && need <= 16) GO(T, (G <= 16 ? G : 16), 16, C);                                              \
-    else if (G <= 8 && need <= 32) GO(T, (G <= 8 ? G : 8), 32, C);                                                 \
-    else if (G <= 4 && need <= 64) GO(T, (G <= 4 ? G : 4), 64, C);                                                 \
-    else return TVB_BAD_ARGUMENT
+    if (few) GO(T, G, 4, C);                                                                                       \
+    else GO(T, G, 8, C)
 #define BY_LANES(T, C)                                                                                             \
     if (lanes == 4) { BY_ROWS(T, 4, C); }                                                                          \
     else if (lanes == 8) { BY_ROWS(T, 8, C); }                                                                     \
@@ -378,8 +437,12 @@ extern "C" int tvb_retention_scan(const float* q, const float* k, const void* v,
     else return TVB_BAD_ARGUMENT;
     if (segment > 0) {
         const int per = dim * vdim;
-        retention_combine_kernel<<<dim3((per + 255) / 256, heads, rows), 256, 0, s>>>(
-            state, parts, decay, row_starts, state_slots, token_row, segment, heads, per);
+        if (per % 4 == 0 && (((uintptr_t)state | (uintptr_t)parts) & 15) == 0)
+            retention_combine_kernel<4><<<dim3((per / 4 + 255) / 256, heads, rows), 256, 0, s>>>(
+                state, parts, decay, row_starts, state_slots, token_row, segment, heads, per);
+        else
+            retention_combine_kernel<1><<<dim3((per + 255) / 256, heads, rows), 256, 0, s>>>(
+                state, parts, decay, row_starts, state_slots, token_row, segment, heads, per);
         BY_LANES(float, true)                     // the correcting pass reads no values: one type will do
     }
 #undef BY_LANES

@@ -751,14 +751,21 @@ RETENTION_ACTS = {None: 0, "silu": 1, "sigmoid": 2}
 SM_COUNT = 148                    # a B200's SMs: what the choice of a piece's size fills
 
 
-def retention_segment(tokens: int, rows: int, heads: int, vdim: int) -> int:
-    """Tokens a piece of the scan.  0 (whole entries) where the entries' (head, 32 columns) CTAs already give
-    every other SM one: the scan is bound by shared-memory reads an SM, not by waiting, and pieces add the
-    correcting pass (measured: 16 heads of 128 gain a third, 32 heads lose a sixth).  Else, for prompts, the
-    longest of 256, 128 and 64 tokens that gives the SMs four CTAs each."""
-    per_piece = heads * -(-vdim // 32)
-    if 2 * rows * per_piece >= SM_COUNT or tokens < 4 * max(rows, 1) or tokens < 256:
+def retention_lanes(dim: int) -> int:
+    """Lanes that share a tile of eight columns of the state: the fewest of 4, 8, 16 and 32 that hold the key
+    with at most eight rows a lane."""
+    return next((lanes for lanes in (4, 8, 16) if lanes * 8 >= dim), 32)
+
+
+def retention_segment(tokens: int, rows: int, heads: int, dim: int, vdim: int) -> int:
+    """Tokens a piece of the scan.  0 (whole entries) for steps of short entries, and where the entries'
+    (head, 32 columns) CTAs, the narrowest there are, already give three SMs in two one.  Else, for
+    prompts, the longest of 256, 128 and 64 tokens that gives the SMs four CTAs each: the pieces cost a
+    correcting pass, a third of the scan's arithmetic, and fill SMs that whole entries leave idle (measured
+    at 2,048 tokens with heads of 128: 16 heads 2.2 times and 32 heads 1.3 times as fast, 64 heads slower)."""
+    if 2 * rows * heads * -(-vdim // 32) >= 3 * SM_COUNT or tokens < 4 * max(rows, 1) or tokens < 256:
         return 0
+    per_piece = heads * -(-vdim // (128 // retention_lanes(dim) * 8))
     segment = 256
     while segment > 64 and (tokens // segment) * per_piece < 4 * SM_COUNT:
         segment //= 2
@@ -782,8 +789,8 @@ def retention(proj: torch.Tensor, *, q_at: int, k_at: int, v_at: int, g_at: int 
     position * ``inv_freq`` on their first ``rot_dims`` dimensions and k is multiplied by ``key_scale``,
     all in float32.  Every head's o is divided by its root mean square (``unit_norm``, with ``eps``),
     multiplied by act(gate) and rounded to the projection's type: [tokens, heads * vdim].  ``raw_out``
-    (float32 [tokens, heads * vdim]) receives o itself.  ``lanes`` (4, 8, 16 or 32, at most a quarter of
-    ``dim``; 0: as many as give every SM work) is the number of lanes that share a column of the state.
+    (float32 [tokens, heads * vdim]) receives o itself.  ``lanes`` (4, 8, 16 or 32, at least an eighth of
+    ``dim``; 0: the fewest, or more where SMs would idle) is the number of lanes that share a tile of eight columns of the state.
 
     ``segment``: 0 walks every entry token by token in one CTA a (head, block of columns); n > 0 cuts the
     entries into pieces of n tokens that run side by side from a state of zero, joins the pieces' states
@@ -824,7 +831,7 @@ def retention(proj: torch.Tensor, *, q_at: int, k_at: int, v_at: int, g_at: int 
         raise KernelError("retention: raw_out must be contiguous float32 [tokens, heads * vdim]")
     turned = torch.empty((2, tokens, heads * dim), dtype=torch.float32, device=proj.device)
     if segment is None:
-        segment = retention_segment(tokens, rows, heads, vdim)
+        segment = retention_segment(tokens, rows, heads, dim, vdim)
     if segment < 0:
         raise KernelError("retention: a piece has at least one token")
     pieces = tokens // segment + rows if segment else 0
