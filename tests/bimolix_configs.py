@@ -81,9 +81,19 @@ BIMOLIX_CONFIGS = {
         _r(1, 5, 3, (0.96875,), (2, 50.0), _moe(4, 2, 6, 1.0, groups=1, keep=1)),
         _a(1, 1, 12, 33, 9, 20.0, _moe(4, 2, 6, 1.0, groups=2, keep=1, shared=3, shared_limit=2.0)),
         _r(5, 4, 4, (1.0, 0.5, 0.9, 0.99, 0.999), (4, 7.0), _dense(11)))),
+    # sizes of the usual kind (powers of two, heads of 64) with an attention layer first, values wider than
+    # keys in the retention layers, experts in a retention layer, a chunk of several pages that long prompts
+    # cross three times, and a table whose reach is the chunk
+    "e": BimolixConfig(vocab=300, width=256, norm_eps=1e-6, layers=(
+        _a(8, 2, 64, 128, 16, 128.0, _dense(512)),
+        _r(4, 64, 128, (0.9375, 0.984375, 0.99609375, 0.9990234375), (64, 10000.0),
+           _moe(8, 2, 64, 2.0, groups=4, keep=2, shared=64, shared_limit=2.0, scale=1.5)),
+        _r(4, 64, 128, (0.9375, 0.984375, 0.99609375, 0.9990234375), (64, 10000.0),
+           _moe(8, 2, 64, 2.0, groups=4, keep=2, shared=64, shared_limit=2.0, scale=1.5), weights_of=1),
+        _a(8, 2, 64, 128, 16, 128.0, _dense(512), weights_of=0))),
 }
-BIMOLIX_SEEDS = {"a": 31, "b": 32, "c": 33, "d": 34}
-BIMOLIX_PAGES = {"a": 16, "b": 8, "c": 16, "d": 4}
+BIMOLIX_SEEDS = {"a": 31, "b": 32, "c": 33, "d": 34, "e": 35}
+BIMOLIX_PAGES = {"a": 16, "b": 8, "c": 16, "d": 4, "e": 32}
 
 
 def tensors_of(config: BimolixConfig, seed: int) -> dict:

@@ -169,7 +169,8 @@ STANDOUTS = {
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("kind", ["rows", "split", "tiles", "singles"])
 @pytest.mark.parametrize("segment", [96, 50, None])
-@pytest.mark.parametrize("heads,kv,dk", [(4, 2, 16), (3, 1, 12), (8, 8, 32), (40, 2, 16), (6, 3, 48)])
+@pytest.mark.parametrize("heads,kv,dk", [(4, 2, 16), (3, 1, 12), (8, 8, 32), (40, 2, 16), (9, 3, 48), (4, 2, 64),
+                                         (2, 1, 128)])
 def test_attention_in_chunks_with_a_distance_table_and_one_more_term(heads, kv, dk, segment, kind, dtype):
     """Random scores plus one key per checked query whose score is a hundred: seen, it takes the whole
     weight; not seen (the last key of the chunk before), it must leave no trace.  The table adds a number
@@ -248,7 +249,7 @@ def test_attention_in_chunks_with_a_distance_table_and_one_more_term(heads, kv, 
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("heads,kv,dim", [(4, 2, 16), (3, 1, 9), (6, 3, 48), (2, 2, 130)])
+@pytest.mark.parametrize("heads,kv,dim", [(4, 2, 16), (3, 1, 9), (9, 3, 48), (2, 2, 130)])
 def test_biases_norm_a_head_and_values_that_are_the_keys(heads, kv, dim, dtype):
     """q and k get their biases, then a weighted RMS norm a head; the value cache receives k with its bias
     and without the norm."""
