@@ -10,7 +10,7 @@
 //   latent_prepare    from a packed projection row [.. dq .. | .. dkv ..]: the query latent
 //                     RMSnorm(dq) * w_q to a buffer; the key/value latent RMSnorm(dkv[:rank]) * w_kv and
 //                     the rotated rest of dkv side by side, [latent | rotated], to the token's cache slot
-//   rotate_heads      pairs (2i, 2i + 1) of a slice of every head turned by position * inv_freq[i],
+//   rotate_heads      pairs (2i, 2i + 1) (or, with `halves`, (i, i + rot_dim / 2)) of a slice of every head turned by position * inv_freq[i],
 //                     cosine and sine times `magnitude`, from one strided layout to another
 //   head_product      out[t, h, j] = sum_k x[t, h, k] * w[h, j, k], optionally times sigmoid(gate[t, h, j]):
 //                     one small product a head (the up-projections of latent attention, folded into the
@@ -213,7 +213,7 @@ __global__ void latent_prepare_kernel(const T* proj, int64_t stride, int dq_at, 
                                       T* __restrict__ q_latent, int64_t q_latent_stride, int dkv_at, int kv_rank,
                                       const W* __restrict__ kv_weight, int rot_dim, const float* __restrict__ inv_freq,
                                       float magnitude, const int* __restrict__ positions,
-                                      const int* __restrict__ slots, T* __restrict__ cache, float eps) {
+                                      const int* __restrict__ slots, T* __restrict__ cache, float eps, int halves) {
     __shared__ float scratch[32];
     const int token = blockIdx.x;
     const T* row = proj + (int64_t)token * stride;
@@ -243,11 +243,13 @@ __global__ void latent_prepare_kernel(const T* proj, int64_t stride, int dq_at, 
         dst[i] = from_float<T>(__fmul_rn(__fmul_rn(to_float<T>(row[dkv_at + i]), inverse), to_float<W>(kv_weight[i])));
     const float position = (float)positions[token];
     for (int i = threadIdx.x; i < rot_dim / 2; i += blockDim.x) {
+        // pair i: elements (2i, 2i + 1), or with `halves` (i, i + rot_dim / 2)
+        const int first = halves ? i : 2 * i, second = halves ? i + rot_dim / 2 : 2 * i + 1;
         float a, b;
-        turn_pair(to_float<T>(row[dkv_at + kv_rank + 2 * i]), to_float<T>(row[dkv_at + kv_rank + 2 * i + 1]),
+        turn_pair(to_float<T>(row[dkv_at + kv_rank + first]), to_float<T>(row[dkv_at + kv_rank + second]),
                   __fmul_rn(position, inv_freq[i]), magnitude, a, b);
-        dst[kv_rank + 2 * i] = from_float<T>(a);
-        dst[kv_rank + 2 * i + 1] = from_float<T>(b);
+        dst[kv_rank + first] = from_float<T>(a);
+        dst[kv_rank + second] = from_float<T>(b);
     }
 }
 
@@ -256,7 +258,7 @@ extern "C" int tvb_latent_prepare(const void* proj, long long stride, int dq_at,
                                   void* q_latent, long long q_latent_stride, int dkv_at, int kv_rank,
                                   const void* kv_weight, int weight_dtype, int rot_dim, const float* inv_freq,
                                   float magnitude, const int* positions, const int* slots, void* cache, float eps,
-                                  int tokens, int dtype, void* stream) {
+                                  int tokens, int dtype, int halves, void* stream) {
     if (tokens <= 0) return 0;
     if (q_rank < 0 || kv_rank <= 0 || rot_dim < 0 || rot_dim % 2 || !kv_weight || !positions ||
         (q_rank > 0 && (!q_weight || !q_latent)) || (rot_dim > 0 && !inv_freq) || (slots && !cache))
@@ -266,7 +268,7 @@ extern "C" int tvb_latent_prepare(const void* proj, long long stride, int dq_at,
     const int threads = widest >= 1024 ? 256 : (widest >= 256 ? 128 : 64);
 #define GO(T, W) latent_prepare_kernel<T, W><<<tokens, threads, 0, s>>>(                                        \
         (const T*)proj, stride, dq_at, q_rank, (const W*)q_weight, (T*)q_latent, q_latent_stride, dkv_at,      \
-        kv_rank, (const W*)kv_weight, rot_dim, inv_freq, magnitude, positions, slots, (T*)cache, eps)
+        kv_rank, (const W*)kv_weight, rot_dim, inv_freq, magnitude, positions, slots, (T*)cache, eps, halves)
     if (dtype == TVB_F32 && weight_dtype == TVB_F32) GO(float, float);
     else if (dtype == TVB_BF16 && weight_dtype == TVB_BF16) GO(bf16, bf16);
     else if (dtype == TVB_BF16 && weight_dtype == TVB_F32) GO(bf16, float);
@@ -280,26 +282,27 @@ template <typename T>
 __global__ void rotate_heads_kernel(const T* src, int64_t src_token_stride, int64_t src_head_stride, T* dst,
                                     int64_t dst_token_stride, int64_t dst_head_stride, int heads, int rot_dim,
                                     const float* __restrict__ inv_freq, float magnitude,
-                                    const int* __restrict__ positions, int64_t pairs) {
+                                    const int* __restrict__ positions, int64_t pairs, int halves) {
     const int64_t index = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (index >= pairs) return;
     const int half = rot_dim / 2;
     const int i = (int)(index % half);
     const int head = (int)((index / half) % heads);
     const int64_t token = index / ((int64_t)half * heads);
-    const T* from = src + token * src_token_stride + head * src_head_stride + 2 * i;
-    T* to = dst + token * dst_token_stride + head * dst_head_stride + 2 * i;
+    const int first = halves ? i : 2 * i, second = halves ? i + half : 2 * i + 1;
+    const T* from = src + token * src_token_stride + head * src_head_stride;
+    T* to = dst + token * dst_token_stride + head * dst_head_stride;
     float a, b;
-    turn_pair(to_float<T>(from[0]), to_float<T>(from[1]), __fmul_rn((float)max(positions[token], 0), inv_freq[i]),
-              magnitude, a, b);
-    to[0] = from_float<T>(a);
-    to[1] = from_float<T>(b);
+    turn_pair(to_float<T>(from[first]), to_float<T>(from[second]),
+              __fmul_rn((float)max(positions[token], 0), inv_freq[i]), magnitude, a, b);
+    to[first] = from_float<T>(a);
+    to[second] = from_float<T>(b);
 }
 
 extern "C" int tvb_rotate_heads(const void* src, long long src_token_stride, long long src_head_stride, void* dst,
                                 long long dst_token_stride, long long dst_head_stride, int heads, int rot_dim,
                                 const float* inv_freq, float magnitude, const int* positions, int tokens, int dtype,
-                                void* stream) {
+                                int halves, void* stream) {
     if (tokens <= 0 || rot_dim == 0) return 0;
     if (heads <= 0 || rot_dim < 0 || rot_dim % 2 || !inv_freq || !positions) return TVB_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
@@ -308,7 +311,7 @@ extern "C" int tvb_rotate_heads(const void* src, long long src_token_stride, lon
     if (blocks > 2147483647LL) return TVB_BAD_ARGUMENT;
 #define GO(T) rotate_heads_kernel<T><<<(unsigned)blocks, 256, 0, s>>>(                                          \
         (const T*)src, src_token_stride, src_head_stride, (T*)dst, dst_token_stride, dst_head_stride, heads,    \
-        rot_dim, inv_freq, magnitude, positions, pairs)
+        rot_dim, inv_freq, magnitude, positions, pairs, halves)
     if (dtype == TVB_F32) GO(float);
     else if (dtype == TVB_BF16) GO(bf16);
     else return TVB_BAD_ARGUMENT;

@@ -22,6 +22,16 @@
 // storage type; only v and the gate are read in it and only the finished output is rounded to it.
 #include "common.cuh"
 
+// RET_GATED (a macro, a library each): 0, the form above; 1, a decay a token and key channel instead of one a
+// head, read from `gates` [tokens, heads * dim] (float32), with the keys tied to it, k = 1 - gate:
+//   S_t = diag(g_t) S_(t-1) + (1 - g_t) v_t^T
+// (a forget gate that also decides what is written); 2, such decays beside keys of their own.  In the pieces
+// form the decay of a piece is the product of its tokens' gates, channel by channel, and the correcting pass
+// reads queries that a kernel of its own multiplied by the running products.
+#ifndef RET_GATED
+#define RET_GATED 0
+#endif
+
 #define RET_PAIR_INTERLEAVED 0
 #define RET_PAIR_HALF_SPLIT 1
 #define RET_MAX_TURNED 512        // pairs of a head that turn: sine and cosine of a token in shared memory
@@ -74,7 +84,8 @@ __global__ void __launch_bounds__(128) retention_prepare_kernel(
 // other half, so that after log2(GROUPS) steps lane g holds sums g * RET_SUMS / GROUPS and on, complete.
 template <typename T, int GROUPS, int ROWS, bool CORRECT>
 __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
-    const float* __restrict__ q, const float* __restrict__ k, const T* __restrict__ v, int64_t v_stride,
+    const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ gates,
+    const T* __restrict__ v, int64_t v_stride,
     float* __restrict__ state, const float* __restrict__ decay, const int* __restrict__ row_starts,
     const int* __restrict__ state_slots, const int* __restrict__ token_row, float* __restrict__ out,
     float* __restrict__ parts, int segment, int rows, int heads, int dim, int vdim) {
@@ -85,7 +96,10 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
     constexpr int LEFT = RET_SUMS / GROUPS;                                 // sums a lane ends with
     static_assert(ROWS % 4 == 0 && RET_SUMS % GROUPS == 0 && RET_BLOCK * COLS % RET_THREADS == 0, "retention_scan: tile");
     __shared__ __align__(16) float q_s[RET_BLOCK][WIDTH];
-    __shared__ __align__(16) float k_s[CORRECT ? 1 : RET_BLOCK][CORRECT ? 4 : WIDTH];
+    constexpr bool KEYS = !CORRECT && RET_GATED != 1;        // keys of their own wait in shared memory
+    constexpr bool GATES = !CORRECT && RET_GATED != 0;       // a decay a token and channel does
+    __shared__ __align__(16) float k_s[KEYS ? RET_BLOCK : 1][KEYS ? WIDTH : 4];
+    __shared__ __align__(16) float g_s[GATES ? RET_BLOCK : 1][GATES ? WIDTH : 4];
     __shared__ __align__(16) float v_s[CORRECT ? 1 : RET_BLOCK][CORRECT ? 4 : COLS];
     __shared__ float power_s[2][RET_BLOCK];    // decay^(t + 1) of this block's tokens and of the next's
     const int head = blockIdx.y, col0 = blockIdx.z * COLS;
@@ -119,7 +133,7 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
                     if (c + cc < vdim) out[(int64_t)(begin + t) * out_stride + (int64_t)head * vdim + c + cc] = 0.0f;
         return;
     }
-    const float a = decay[head];
+    const float a = RET_GATED ? 1.0f : decay[head];
     // whole entries start from and leave the request's state; a piece starts from nothing and leaves what
     // its tokens add (`parts`), which the combine kernel turns into the state the piece starts from: the
     // correcting pass reads that and adds what it gives to every token of the piece
@@ -155,9 +169,10 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
     if (CORRECT && !__syncthreads_or(any)) return;            // the request's first piece: nothing came before
     const int64_t qk_stride = (int64_t)heads * dim;
     const float* q_head = q + (int64_t)begin * qk_stride + (int64_t)head * dim;
-    const float* k_head = k + (int64_t)begin * qk_stride + (int64_t)head * dim;
+    const float* k_head = KEYS ? k + (int64_t)begin * qk_stride + (int64_t)head * dim : nullptr;
+    const float* g_head = GATES ? gates + (int64_t)begin * qk_stride + (int64_t)head * dim : nullptr;
     const T* v_head = v + (int64_t)begin * v_stride + (int64_t)head * vdim + col0;
-    float q_next[LOADS], k_next[LOADS], v_next[V_LOADS];
+    float q_next[LOADS], k_next[KEYS ? LOADS : 1], g_next[GATES ? LOADS : 1], v_next[V_LOADS];
 
     auto fetch = [&](int first) {                 // tokens first .. first + RET_BLOCK - 1 into registers
 #pragma unroll
@@ -165,7 +180,8 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
             const int e = tid + RET_THREADS * j, t = e / WIDTH, d = e % WIDTH;
             const bool ok = e < RET_BLOCK * WIDTH && first + t < count && d < dim;
             q_next[j] = ok ? q_head[(int64_t)(first + t) * qk_stride + d] : 0.0f;
-            if constexpr (!CORRECT) k_next[j] = ok ? k_head[(int64_t)(first + t) * qk_stride + d] : 0.0f;
+            if constexpr (KEYS) k_next[j] = ok ? k_head[(int64_t)(first + t) * qk_stride + d] : 0.0f;
+            if constexpr (GATES) g_next[j] = ok ? g_head[(int64_t)(first + t) * qk_stride + d] : 0.0f;
         }
         if constexpr (!CORRECT) {
 #pragma unroll
@@ -182,7 +198,8 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
             const int e = tid + RET_THREADS * j;
             if (e < RET_BLOCK * WIDTH) {
                 q_s[e / WIDTH][e % WIDTH] = q_next[j];
-                if constexpr (!CORRECT) k_s[e / WIDTH][e % WIDTH] = k_next[j];
+                if constexpr (KEYS) k_s[e / WIDTH][e % WIDTH] = k_next[j];
+                if constexpr (GATES) g_s[e / WIDTH][e % WIDTH] = g_next[j];
             }
         }
         if constexpr (!CORRECT) {
@@ -195,14 +212,14 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
     };
 
     fetch(0);
-    if (CORRECT && tid < RET_BLOCK) power_s[0][tid] = powf(a, (float)(tid + 1));
+    if (CORRECT && !RET_GATED && tid < RET_BLOCK) power_s[0][tid] = powf(a, (float)(tid + 1));
     for (int first = 0; first < count; first += RET_BLOCK) {
         const int turn = (first / RET_BLOCK) & 1;
         __syncthreads();                          // the block before is read
         stage();
         __syncthreads();
         if (first + RET_BLOCK < count) fetch(first + RET_BLOCK);
-        if (CORRECT && tid < RET_BLOCK) power_s[turn ^ 1][tid] = powf(a, (float)(first + RET_BLOCK + tid + 1));
+        if (CORRECT && !RET_GATED && tid < RET_BLOCK) power_s[turn ^ 1][tid] = powf(a, (float)(first + RET_BLOCK + tid + 1));
         const int here = min(RET_BLOCK, count - first);
         float sums[RET_SUMS];
 #pragma unroll
@@ -223,13 +240,23 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
                     const float4 qq = *reinterpret_cast<const float4*>(&q_s[t][4 * (group + GROUPS * j)]);
                     const float qr[4] = {qq.x, qq.y, qq.z, qq.w};
                     if constexpr (!CORRECT) {
-                        const float4 kk = *reinterpret_cast<const float4*>(&k_s[t][4 * (group + GROUPS * j)]);
-                        const float kr[4] = {kk.x, kk.y, kk.z, kk.w};
+                        float kr[4], gr[4] = {a, a, a, a};
+                        if constexpr (GATES) {
+                            const float4 gg = *reinterpret_cast<const float4*>(&g_s[t][4 * (group + GROUPS * j)]);
+                            gr[0] = gg.x; gr[1] = gg.y; gr[2] = gg.z; gr[3] = gg.w;
+                        }
+                        if constexpr (KEYS) {
+                            const float4 kk = *reinterpret_cast<const float4*>(&k_s[t][4 * (group + GROUPS * j)]);
+                            kr[0] = kk.x; kr[1] = kk.y; kr[2] = kk.z; kr[3] = kk.w;
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) kr[i] = __fsub_rn(1.0f, gr[i]);      // what is not kept is written
+                        }
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
 #pragma unroll
                             for (int cc = 0; cc < RET_TILE; ++cc)
-                                s[4 * j + i][cc] = __fmaf_rn(kr[i], vv[cc], __fmul_rn(a, s[4 * j + i][cc]));
+                                s[4 * j + i][cc] = __fmaf_rn(kr[i], vv[cc], __fmul_rn(gr[i], s[4 * j + i][cc]));
                     }
 #pragma unroll
                     for (int i = 0; i < 4; ++i)
@@ -255,7 +282,8 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
             const int index = group * LEFT + i, t = index / RET_TILE, cc = index % RET_TILE;
             if (t < here && c + cc < vdim) {
                 float* o = out + (int64_t)(begin + first + t) * out_stride + (int64_t)head * vdim + c + cc;
-                *o = CORRECT ? __fmaf_rn(power_s[turn][t], sums[i], *o) : sums[i];     // decay^(t + 1) S_0^T q_t
+                // decay^(t + 1) S_0^T q_t; with gates the queries came multiplied by the running products
+                *o = CORRECT ? (RET_GATED ? __fadd_rn(*o, sums[i]) : __fmaf_rn(power_s[turn][t], sums[i], *o)) : sums[i];
             }
         }
     }
@@ -288,8 +316,8 @@ __global__ void __launch_bounds__(RET_THREADS) retention_scan_kernel(
 template <int VEC>                                // elements a thread: 4 (float4s, where rows of 4 fit) or 1
 __global__ void __launch_bounds__(256) retention_combine_kernel(
     float* __restrict__ state, float* __restrict__ parts, const float* __restrict__ decay,
-    const int* __restrict__ row_starts, const int* __restrict__ state_slots, const int* __restrict__ token_row,
-    int segment, int heads, int per) {
+    const float* __restrict__ piece_gates, const int* __restrict__ row_starts, const int* __restrict__ state_slots,
+    const int* __restrict__ token_row, int segment, int heads, int per, int vdim) {
     const int row = blockIdx.z, head = blockIdx.y, e = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (e >= per) return;
     int before = 0;
@@ -297,9 +325,17 @@ __global__ void __launch_bounds__(256) retention_combine_kernel(
     const int begin = row_starts[row], tokens = row_starts[row + 1] - begin;
     if (tokens <= 0 || token_row[begin] < 0) return;
     const int pieces = (tokens + segment - 1) / segment;
+#if RET_GATED
+    // the decay of a piece: the product of its tokens' gates in this element's key channel (VEC elements lie in
+    // one row of the state)
+    const int dim = per / vdim;
+    const float* gate_of = piece_gates + ((int64_t)before * heads + head) * dim + e / vdim;
+    const int64_t gates_apart = (int64_t)heads * dim;
+#else
     const float a = decay[head];
     const float whole = powf(a, (float)segment);
     const float rest = powf(a, (float)(tokens - (pieces - 1) * segment));      // the last piece may be shorter
+#endif
     float* mine = state + ((int64_t)state_slots[row] * heads + head) * per + e;
     float* first = parts + ((int64_t)before * heads + head) * per + e;
     const int64_t apart = (int64_t)heads * per;
@@ -315,14 +351,26 @@ __global__ void __launch_bounds__(256) retention_combine_kernel(
     load(mine, s);
     for (int j0 = 0; j0 < pieces; j0 += 8) {      // eight pieces' loads are in flight together
         float added[8][VEC];
+#if RET_GATED
+        float powers[8];
+#endif
 #pragma unroll
         for (int u = 0; u < 8; ++u)
-            if (j0 + u < pieces) load(first + (j0 + u) * apart, added[u]);
+            if (j0 + u < pieces) {
+                load(first + (j0 + u) * apart, added[u]);
+#if RET_GATED
+                powers[u] = gate_of[(j0 + u) * gates_apart];
+#endif
+            }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             if (j0 + u >= pieces) break;
             store(first + (j0 + u) * apart, s);
+#if RET_GATED
+            const float power = powers[u];
+#else
             const float power = j0 + u == pieces - 1 ? rest : whole;
+#endif
 #pragma unroll
             for (int i = 0; i < VEC; ++i) s[i] = __fmaf_rn(power, s[i], added[u][i]);
         }
@@ -330,15 +378,98 @@ __global__ void __launch_bounds__(256) retention_combine_kernel(
     store(mine, s);
 }
 
+// With a decay a token and channel: the running product of a piece's gates, channel by channel.  A thread walks
+// one channel of one head through one piece, leaves q_t times the product up to and with token t (what the
+// correcting pass multiplies with the state the piece starts from) and, at the end, the piece's whole product.
+__global__ void __launch_bounds__(128) retention_gate_prefix_kernel(
+    const float* __restrict__ q, const float* __restrict__ gates, float* __restrict__ scaled_q,
+    float* __restrict__ piece_gates, const int* __restrict__ row_starts, const int* __restrict__ token_row,
+    int segment, int rows, int heads, int dim) {
+    const int head = blockIdx.y;
+    int row, before = 0, tokens = 0;
+    for (row = 0; row < rows; ++row) {
+        tokens = row_starts[row + 1] - row_starts[row];
+        const int pieces = (tokens + segment - 1) / segment;
+        if ((int)blockIdx.x < before + pieces) break;
+        before += pieces;
+    }
+    if (row == rows) return;
+    const int piece = blockIdx.x - before;
+    const int begin = row_starts[row] + piece * segment;
+    const int count = min(segment, tokens - piece * segment);
+    if (count <= 0 || token_row[begin] < 0) return;
+    const int64_t stride = (int64_t)heads * dim;
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+        const int64_t at = (int64_t)begin * stride + (int64_t)head * dim + d;
+        float product = 1.0f;
+        for (int t0 = 0; t0 < count; t0 += 8) {           // eight tokens' loads are in flight together
+            float g[8], x[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (t0 + u < count) { g[u] = gates[at + (t0 + u) * stride]; x[u] = q[at + (t0 + u) * stride]; }
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (t0 + u < count) {
+                    product = __fmul_rn(product, g[u]);
+                    scaled_q[at + (t0 + u) * stride] = __fmul_rn(x[u], product);
+                }
+        }
+        piece_gates[((int64_t)blockIdx.x * heads + head) * dim + d] = product;
+    }
+}
+
+// What a recurrence with a gate a channel reads, from a packed projection: q = act(projection) (act none or SiLU)
+// and g = lower + (1 - lower) * sigmoid(projection + bias), a gate that never falls below `lower`; both float32
+// [tokens, per].  `bias` and `lower` (float32 [per]) may be null: 0.
+template <typename T>
+__global__ void __launch_bounds__(256) gated_prepare_kernel(
+    const T* __restrict__ proj, int64_t token_stride, int q_at, int g_at, int per, const float* __restrict__ bias,
+    const float* __restrict__ lower, int q_act, float* __restrict__ q_out, float* __restrict__ g_out) {
+    const int token = blockIdx.y;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= per) return;
+    const T* row = proj + (int64_t)token * token_stride;
+    const float x = to_float<T>(row[q_at + e]);
+    q_out[(int64_t)token * per + e] = q_act ? __fdiv_rn(x, __fadd_rn(1.0f, expf(-x))) : x;
+    float z = to_float<T>(row[g_at + e]);
+    if (bias) z = __fadd_rn(z, bias[e]);
+    const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-z)));
+    const float low = lower ? lower[e] : 0.0f;
+    g_out[(int64_t)token * per + e] = __fmaf_rn(__fsub_rn(1.0f, low), sig, low);
+}
+
+extern "C" int tvb_gated_prepare(const void* proj, long long token_stride, int q_at, int g_at, int per,
+                                 const float* bias, const float* lower, int q_act, float* q_out, float* g_out,
+                                 int tokens, int dtype, void* stream) {
+    if (tokens <= 0) return 0;
+    if (per <= 0 || q_at < 0 || g_at < 0 || !q_out || !g_out) return TVB_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    for (int first = 0; first < tokens; first += 65535) {
+        const int count = min(65535, tokens - first);
+        const dim3 grid((per + 255) / 256, count);
+        if (dtype == TVB_F32)
+            gated_prepare_kernel<float><<<grid, 256, 0, s>>>((const float*)proj + (int64_t)first * token_stride, token_stride,
+                                                            q_at, g_at, per, bias, lower, q_act, q_out + (int64_t)first * per,
+                                                            g_out + (int64_t)first * per);
+        else if (dtype == TVB_BF16)
+            gated_prepare_kernel<bf16><<<grid, 256, 0, s>>>((const bf16*)proj + (int64_t)first * token_stride, token_stride,
+                                                           q_at, g_at, per, bias, lower, q_act, q_out + (int64_t)first * per,
+                                                           g_out + (int64_t)first * per);
+        else return TVB_BAD_ARGUMENT;
+    }
+    return tvb_last_error();
+}
+
 #define RET_ACT_NONE 0
 #define RET_ACT_SILU 1
 #define RET_ACT_SIGMOID 2
 
-// A warp a (token, head): o / sqrt(mean(o^2) + eps) (with `unit_norm`), times act(gate).
+// A warp a (token, head): o / sqrt(mean(o^2) + eps) (with `unit_norm`; times `norm_weight` [vdim], one for all
+// heads, if given), times act(gate).
 template <typename T>
 __global__ void __launch_bounds__(128) retention_finish_kernel(
     const float* __restrict__ o, const T* gate, int64_t gate_stride, T* __restrict__ out, int64_t out_stride,
-    int tokens, int heads, int vdim, int unit_norm, float eps, int act) {
+    int tokens, int heads, int vdim, int unit_norm, float eps, int act, const float* __restrict__ norm_weight) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t item = (int64_t)blockIdx.x * 4 + warp;
     if (item >= (int64_t)tokens * heads) return;
@@ -355,6 +486,7 @@ __global__ void __launch_bounds__(128) retention_finish_kernel(
     T* dst = out + (int64_t)token * out_stride + (int64_t)head * vdim;
     for (int i = lane; i < vdim; i += 32) {
         float x = __fmul_rn(src[i], factor);
+        if (norm_weight) x = __fmul_rn(x, norm_weight[i]);
         if (g) {
             const float z = to_float<T>(g[i]);
             const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-z)));
@@ -400,14 +532,24 @@ extern "C" int tvb_retention_max_dim() { return 256; }
 // parts [pieces, heads, dim, vdim], what the piece adds; then the states the pieces start from, along every
 // entry; then decay^(t + 1) S_start^T q_t added to the piece's token t.  `pieces` is at least the number of
 // pieces of all entries (tokens / segment + rows always is).
+//
+// A library compiled with RET_GATED takes `gates` (float32 [tokens, heads * dim]) instead of `decay`, and with
+// RET_GATED == 1 no `k`; in pieces it also wants `scaled_q` (float32, the size of q) and `piece_gates` (float32
+// [pieces, heads, dim]) as scratch.
 extern "C" int tvb_retention_scan(const float* q, const float* k, const void* v, long long v_stride, float* state,
                                   const float* decay, const int* row_starts, const int* state_slots,
                                   const int* token_row, float* out, int rows, int heads, int dim, int vdim,
-                                  int lanes, float* parts, int segment, int pieces, int dtype, void* stream) {
+                                  int lanes, float* parts, int segment, int pieces, int dtype,
+                                  const float* gates, float* scaled_q, float* piece_gates, void* stream) {
     if (rows <= 0) return 0;
     if (heads <= 0 || heads > 65535 || dim <= 0 || dim > 256 || vdim <= 0 || rows > 65535 || segment < 0 ||
         (segment > 0 && (!parts || pieces <= 0)))
         return TVB_BAD_ARGUMENT;
+#if RET_GATED
+    if (!gates || (RET_GATED == 2 && !k) || (segment > 0 && (!scaled_q || !piece_gates))) return TVB_BAD_ARGUMENT;
+#else
+    if (!decay || !k || gates) return TVB_BAD_ARGUMENT;
+#endif
     const int blocks = segment > 0 ? pieces : rows;
     if (lanes == 0) {                             // the fewest that hold the key, more while SMs would idle
         for (lanes = 4; lanes < 32 && lanes * 8 < dim; lanes *= 2) {}
@@ -422,8 +564,8 @@ extern "C" int tvb_retention_scan(const float* q, const float* k, const void* v,
     const bool few = (dim + lanes - 1) / lanes <= 4;          // rows of the state a lane: four or eight
     cudaStream_t s = (cudaStream_t)stream;
 #define GO(T, G, R, C) retention_scan_kernel<T, G, R, C><<<grid, RET_THREADS, 0, s>>>(                              \
-        q, k, (const T*)v, v_stride, state, decay, row_starts, state_slots, token_row, out, parts, segment, rows,  \
-        heads, dim, vdim)
+        (C && RET_GATED) ? scaled_q : q, k, gates, (const T*)v, v_stride, state, decay, row_starts, state_slots,   \
+        token_row, out, parts, segment, rows, heads, dim, vdim)
 #define BY_ROWS(T, G, C)                                                                                           \
     if (few) GO(T, G, 4, C);                                                                                       \
     else GO(T, G, 8, C)
@@ -437,12 +579,17 @@ extern "C" int tvb_retention_scan(const float* q, const float* k, const void* v,
     else return TVB_BAD_ARGUMENT;
     if (segment > 0) {
         const int per = dim * vdim;
-        if (per % 4 == 0 && (((uintptr_t)state | (uintptr_t)parts) & 15) == 0)
+#if RET_GATED
+        retention_gate_prefix_kernel<<<dim3(pieces, heads), 128, 0, s>>>(q, gates, scaled_q, piece_gates, row_starts,
+                                                                        token_row, segment, rows, heads, dim);
+#endif
+        // four elements a thread where they lie in one row of the state (gates: one decay for the four)
+        if ((RET_GATED ? vdim : per) % 4 == 0 && (((uintptr_t)state | (uintptr_t)parts) & 15) == 0)
             retention_combine_kernel<4><<<dim3((per / 4 + 255) / 256, heads, rows), 256, 0, s>>>(
-                state, parts, decay, row_starts, state_slots, token_row, segment, heads, per);
+                state, parts, decay, piece_gates, row_starts, state_slots, token_row, segment, heads, per, vdim);
         else
             retention_combine_kernel<1><<<dim3((per + 255) / 256, heads, rows), 256, 0, s>>>(
-                state, parts, decay, row_starts, state_slots, token_row, segment, heads, per);
+                state, parts, decay, piece_gates, row_starts, state_slots, token_row, segment, heads, per, vdim);
         BY_LANES(float, true)                     // the correcting pass reads no values: one type will do
     }
 #undef BY_LANES
@@ -454,7 +601,7 @@ extern "C" int tvb_retention_scan(const float* q, const float* k, const void* v,
 // o: float32 [tokens, heads * vdim]; gate (or null) and out of the storage type, rows may be strided.
 extern "C" int tvb_retention_finish(const float* o, const void* gate, long long gate_stride, void* out,
                                     long long out_stride, int tokens, int heads, int vdim, int unit_norm, float eps,
-                                    int act, int dtype, void* stream) {
+                                    int act, const float* norm_weight, int dtype, void* stream) {
     if (tokens <= 0) return 0;
     if (heads <= 0 || vdim <= 0 || act < 0 || act > 2) return TVB_BAD_ARGUMENT;
     const long long blocks = ((long long)tokens * heads + 3) / 4;
@@ -462,10 +609,10 @@ extern "C" int tvb_retention_finish(const float* o, const void* gate, long long 
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == TVB_F32)
         retention_finish_kernel<float><<<(unsigned)blocks, 128, 0, s>>>(o, (const float*)gate, gate_stride, (float*)out,
-                                                                        out_stride, tokens, heads, vdim, unit_norm, eps, act);
+                                                                        out_stride, tokens, heads, vdim, unit_norm, eps, act, norm_weight);
     else if (dtype == TVB_BF16)
         retention_finish_kernel<bf16><<<(unsigned)blocks, 128, 0, s>>>(o, (const bf16*)gate, gate_stride, (bf16*)out,
-                                                                       out_stride, tokens, heads, vdim, unit_norm, eps, act);
+                                                                       out_stride, tokens, heads, vdim, unit_norm, eps, act, norm_weight);
     else return TVB_BAD_ARGUMENT;
     return tvb_last_error();
 }

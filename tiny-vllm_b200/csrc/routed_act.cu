@@ -297,3 +297,143 @@ extern "C" int tvb_route_gated_act(const float* logits, long long logits_stride,
 #undef GO
     return tvb_last_error();
 }
+
+
+// ------------------------------------------------------------------------------------------------
+// Softmax routing over experts and pass-through slots, with a choice correction, and gated experts.
+//
+// Per token, from router logits z (float32, one a slot; the first `experts` slots are experts, the last
+// `identity` slots hand the layer's input on unchanged and have no tensors): s = softmax(z) over all slots;
+// the choice score is s_e + correction_e (`correction` may be null); the `top` slots with the largest choice
+// scores are chosen (of equal scores the lower index wins).  A chosen slot's weight is s_e as it is, or, with
+// `renormalise`, s_e over the sum of the chosen s.
+//
+// The packed projection of a token holds [gate_e | up_e] (ff columns each) expert after expert; column c of
+// expert e of the output holds act(gate) * up times the expert's weight (exactly 0 if the expert was not
+// chosen), act = SiLU.  `identity_out[token]` receives the sum of the chosen pass-through slots' weights: the
+// caller adds that many times the layer's input to the result of the down-projection.
+template <typename T, bool WIDE>
+__global__ void route_softmax_gated_kernel(const float* __restrict__ logits, int64_t logits_stride,
+                                           const float* __restrict__ correction, const T* proj, int64_t proj_stride,
+                                           T* __restrict__ out, int64_t out_stride, float* __restrict__ weights_out,
+                                           float* __restrict__ identity_out, int experts, int identity, int top,
+                                           int renormalise, int ff) {
+    __shared__ float share[ROUTE_MAX_EXPERTS];       // softmax scores, then the weight of every slot, 0 if not chosen
+    __shared__ float value[ROUTE_MAX_EXPERTS];       // choice scores, -inf once chosen
+    __shared__ unsigned char chosen[ROUTE_MAX_EXPERTS];
+    const int64_t token = blockIdx.x;
+    const int slots = experts + identity;
+    const float* z = logits + token * logits_stride;
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float top_logit = -INFINITY;
+        for (int e = lane; e < slots; e += 32) top_logit = fmaxf(top_logit, z[e]);
+#pragma unroll
+        for (int delta = 16; delta > 0; delta >>= 1) top_logit = fmaxf(top_logit, __shfl_xor_sync(0xffffffffu, top_logit, delta));
+        float total = 0.0f;
+        for (int e = lane; e < slots; e += 32) {
+            const float w = expf(__fsub_rn(z[e], top_logit));
+            share[e] = w;
+            total = __fadd_rn(total, w);
+        }
+        total = warp_sum(total);
+        for (int e = lane; e < slots; e += 32) {
+            const float s = __fdiv_rn(share[e], total);
+            share[e] = s;
+            chosen[e] = 0;
+            value[e] = correction ? __fadd_rn(s, correction[e]) : s;
+        }
+        __syncwarp();
+        float sum = 0.0f;
+        for (int round = 0; round < top; ++round) {
+            float best = -INFINITY;
+            int where = ROUTE_MAX_EXPERTS;
+            for (int e = lane; e < slots; e += 32)
+                if (value[e] > best) { best = value[e]; where = e; }
+#pragma unroll
+            for (int delta = 16; delta > 0; delta >>= 1) {
+                const float other = __shfl_xor_sync(0xffffffffu, best, delta);
+                const int other_where = __shfl_xor_sync(0xffffffffu, where, delta);
+                if (other > best || (other == best && other_where < where)) { best = other; where = other_where; }
+            }
+            if (where >= slots) break;                  // fewer slots than `top`
+            sum = __fadd_rn(sum, share[where]);
+            if (lane == 0) { value[where] = -INFINITY; chosen[where] = 1; }
+            __syncwarp();
+        }
+        float passed = 0.0f;
+        for (int e = lane; e < slots; e += 32) {
+            const float w = chosen[e] ? (renormalise ? __fdiv_rn(share[e], sum) : share[e]) : 0.0f;
+            share[e] = w;
+            if (e >= experts) passed = __fadd_rn(passed, w);
+        }
+        passed = warp_sum(passed);
+        if (lane == 0 && identity_out && blockIdx.y == 0) identity_out[token] = passed;
+    }
+    __syncthreads();
+    if (weights_out && blockIdx.y == 0)
+        for (int e = threadIdx.x; e < slots; e += blockDim.x) weights_out[token * slots + e] = share[e];
+    const T* src = proj + token * proj_stride;
+    T* dst = out + token * out_stride;
+    const int routed = experts * ff;
+    int per_block = (routed + gridDim.y - 1) / gridDim.y;
+    if (WIDE) per_block = (per_block + 7) / 8 * 8;
+    const int begin = blockIdx.y * per_block, end = min(routed, begin + per_block);
+    constexpr int STEP = WIDE ? 8 : 1;
+    for (int c = begin + threadIdx.x * STEP; c < end; c += blockDim.x * STEP) {
+        const int e = c / ff;
+        const float weight = share[e];
+        const T* gate = src + (int64_t)e * 2 * ff + (c - e * ff);
+        const T* up = gate + ff;
+        float o[STEP];
+        if (weight == 0.0f) {
+#pragma unroll
+            for (int i = 0; i < STEP; ++i) o[i] = 0.0f;
+        } else {
+            float g[STEP], u[STEP];
+            if constexpr (WIDE) {
+                unpack_bf16x8(ld_global_16(gate), g);
+                unpack_bf16x8(ld_global_16(up), u);
+            } else {
+                g[0] = to_float<T>(gate[0]);
+                u[0] = to_float<T>(up[0]);
+            }
+#pragma unroll
+            for (int i = 0; i < STEP; ++i)
+                o[i] = __fmul_rn(__fmul_rn(__fdiv_rn(g[i], __fadd_rn(1.0f, expf(-g[i]))), u[i]), weight);
+        }
+        if constexpr (WIDE) *reinterpret_cast<uint4*>(dst + c) = pack_bf16x8(o);
+        else dst[c] = from_float<T>(o[0]);
+    }
+}
+
+// logits float32 [tokens, experts + identity]; correction float32 [experts + identity] or null; proj
+// [tokens, 2 * experts * ff] and out [tokens, experts * ff] with row strides; weights_out (optional) float32
+// [tokens, experts + identity]; identity_out (needed with identity > 0) float32 [tokens].
+extern "C" int tvb_route_softmax_gated(const float* logits, long long logits_stride, const float* correction,
+                                       const void* proj, long long proj_stride, void* out, long long out_stride,
+                                       float* weights_out, float* identity_out, int tokens, int experts, int identity,
+                                       int top, int renormalise, int ff, int dtype, void* stream) {
+    if (tokens <= 0) return 0;
+    if (experts <= 0 || identity < 0 || experts + identity > ROUTE_MAX_EXPERTS || top <= 0 || ff <= 0 ||
+        (identity > 0 && !identity_out))
+        return TVB_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long columns = (long long)experts * ff;
+    const int threads = 256;
+    long long split = tokens >= 296 ? 1 : (296 + tokens - 1) / tokens;
+    const long long most = (columns + 4 * threads - 1) / (4 * threads);
+    if (split > most) split = most;
+    if (split > 65535) split = 65535;
+    const dim3 grid(tokens, (unsigned)split);
+    const bool wide = dtype == TVB_BF16 && ff % 8 == 0 && proj_stride % 8 == 0 && out_stride % 8 == 0 &&
+                      (uintptr_t)proj % 16 == 0 && (uintptr_t)out % 16 == 0;
+#define GO(T, WIDE) route_softmax_gated_kernel<T, WIDE><<<grid, threads, 0, s>>>(                                  \
+        logits, logits_stride, correction, (const T*)proj, proj_stride, (T*)out, out_stride, weights_out,          \
+        identity_out, experts, identity, top, renormalise, ff)
+    if (dtype == TVB_F32) GO(float, false);
+    else if (dtype == TVB_BF16) { if (wide) GO(bf16, true); else GO(bf16, false); }
+    else return TVB_BAD_ARGUMENT;
+#undef GO
+    return tvb_last_error();
+}

@@ -80,6 +80,134 @@ extern "C" int tvb_stream_norm(const float* stream_in, const void* add1, const v
     return TVB_BAD_ARGUMENT;
 }
 
+// ---------------------------------------------- a norm after a sublayer and the norm before the next
+//   sandwich_norm   t  = y + scale[row] * x                    (the second term optional)
+//                   s' = s + t * rsqrt(mean(t^2) + eps_post) * w_post     (without w_post: s' = s + t; without y: s' = s)
+//                   out = round_T(s' * rsqrt(mean(s'^2) + eps_pre) * w_pre)   (without w_pre: no out)
+//                   One block per row, all of it float32 with one rounding at the end.  A sublayer's output
+//                   is normed before it joins the stream, and the stream is normed for the next sublayer, in
+//                   one pass over the row.  With `gather` only the named rows are produced and the stream is
+//                   not written.
+//   add_scaled_rows y[row] += scale[row] * x[row]   (float32 y and scale, x of the storage type)
+template <typename Y, typename T, typename W>
+__global__ void sandwich_norm_kernel(const float* stream_in, const Y* y, const float* row_scale, const T* x,
+                                     const W* __restrict__ post_weight, const W* __restrict__ pre_weight,
+                                     T* __restrict__ out, float* stream_out, const int* __restrict__ gather,
+                                     int width, float post_eps, float pre_eps) {
+    extern __shared__ float row_values[];
+    __shared__ float scratch[32];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int out_row = blockIdx.x;
+    const int64_t in_row = gather ? gather[out_row] : out_row;
+    const float* sr = stream_in + in_row * width;
+    float inverse_post = 1.0f;
+    if (y) {
+        const Y* yr = y + in_row * width;
+        const T* xr = (x && row_scale) ? x + in_row * width : nullptr;
+        const float scale = xr ? row_scale[in_row] : 0.0f;
+        float part = 0.0f;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            float t = to_float<Y>(yr[i]);
+            if (xr) t = __fmaf_rn(scale, to_float<T>(xr[i]), t);
+            row_values[i] = t;
+            part = __fmaf_rn(t, t, part);
+        }
+        if (post_weight) {
+            const float total = block_sum(part, scratch);
+            inverse_post = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)width), post_eps)));
+        }
+    }
+    float part = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {          // a thread reads back only what it wrote
+        float v = sr[i];
+        if (y) {
+            float t = row_values[i];
+            if (post_weight) t = __fmul_rn(__fmul_rn(t, inverse_post), to_float<W>(post_weight[i]));
+            v = __fadd_rn(v, t);
+        }
+        row_values[i] = v;
+        part = __fmaf_rn(v, v, part);
+    }
+    float inverse_pre = 1.0f;
+    if (pre_weight) {
+        const float total = block_sum(part, scratch);
+        inverse_pre = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)width), pre_eps)));
+    }
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = row_values[i];
+        if (stream_out && !gather) stream_out[(int64_t)out_row * width + i] = v;
+        if (pre_weight) out[(int64_t)out_row * width + i] =
+            from_float<T>(__fmul_rn(__fmul_rn(v, inverse_pre), to_float<W>(pre_weight[i])));
+    }
+}
+
+template <typename Y, typename T, typename W>
+static int launch_sandwich_norm(const float* stream_in, const void* y, const float* row_scale, const void* x,
+                                const void* post_weight, const void* pre_weight, void* out, float* stream_out,
+                                const int* gather, int rows, int width, float post_eps, float pre_eps, int pdl,
+                                cudaStream_t s) {
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 200 * 1024) return TVB_BAD_ARGUMENT;
+    auto kernel = sandwich_norm_kernel<Y, T, W>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : (width >= 128 ? 128 : 32));
+    TvbLaunch launch(dim3(rows), dim3(threads), smem, s, pdl);
+    cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, stream_in, (const Y*)y, row_scale, (const T*)x,
+                                       (const W*)post_weight, (const W*)pre_weight, (T*)out, stream_out, gather,
+                                       width, post_eps, pre_eps);
+    return e == cudaSuccess ? tvb_last_error() : (int)e;
+}
+
+// y_dtype: type of y; dtype: type of x and out; weight_dtype: type of both norm weights.
+extern "C" int tvb_sandwich_norm(const float* stream_in, const void* y, int y_dtype, const float* row_scale,
+                                 const void* x, const void* post_weight, const void* pre_weight, int weight_dtype,
+                                 void* out, int dtype, float* stream_out, const int* gather, int rows, int width,
+                                 float post_eps, float pre_eps, int pdl, void* stream) {
+    if (rows <= 0) return 0;
+    if (width <= 0 || !stream_in || (pre_weight && !out) || (post_weight && !y) || ((row_scale != nullptr) != (x != nullptr)))
+        return TVB_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+#define GO(Y, T, W) return launch_sandwich_norm<Y, T, W>(stream_in, y, row_scale, x, post_weight, pre_weight, out, \
+                                                         stream_out, gather, rows, width, post_eps, pre_eps, pdl, s)
+    if (dtype == TVB_F32 && weight_dtype == TVB_F32 && y_dtype == TVB_F32) GO(float, float, float);
+    if (dtype == TVB_BF16 && weight_dtype == TVB_BF16 && y_dtype == TVB_F32) GO(float, bf16, bf16);
+    if (dtype == TVB_BF16 && weight_dtype == TVB_F32 && y_dtype == TVB_F32) GO(float, bf16, float);
+    if (dtype == TVB_BF16 && weight_dtype == TVB_BF16 && y_dtype == TVB_BF16) GO(bf16, bf16, bf16);
+    if (dtype == TVB_BF16 && weight_dtype == TVB_F32 && y_dtype == TVB_BF16) GO(bf16, bf16, float);
+#undef GO
+    return TVB_BAD_ARGUMENT;
+}
+
+template <typename T>
+__global__ void add_scaled_rows_kernel(float* __restrict__ y, const T* __restrict__ x, const float* __restrict__ scale,
+                                       int width) {
+    const int64_t row = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < width) y[row * width + i] = __fmaf_rn(scale[row], to_float<T>(x[row * width + i]), y[row * width + i]);
+}
+
+extern "C" int tvb_add_scaled_rows(float* y, const void* x, const float* scale, int rows, int width, int dtype,
+                                   void* stream) {
+    if (rows <= 0) return 0;
+    if (width <= 0) return TVB_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    for (int first = 0; first < rows; first += 65535) {
+        const dim3 grid((width + 255) / 256, min(65535, rows - first));
+        if (dtype == TVB_F32)
+            add_scaled_rows_kernel<float><<<grid, 256, 0, s>>>(y + (int64_t)first * width, (const float*)x + (int64_t)first * width,
+                                                              scale + first, width);
+        else if (dtype == TVB_BF16)
+            add_scaled_rows_kernel<bf16><<<grid, 256, 0, s>>>(y + (int64_t)first * width, (const bf16*)x + (int64_t)first * width,
+                                                             scale + first, width);
+        else return TVB_BAD_ARGUMENT;
+    }
+    return tvb_last_error();
+}
+
 // ------------------------------------------------------------ act(gate) * up
 #define TVB_ACT_SILU 0
 #define TVB_ACT_GELU_TANH 1

@@ -375,17 +375,25 @@ def latent_attention(ctx, mixer, projected: torch.Tensor, run: int) -> torch.Ten
     position = mixer.position
     inv_freq = None if position is None else position.inv_freq
     magnitude = 1.0 if position is None else position.magnitude
+    pairing = "interleaved" if position is None else position.pairing
+    window, sinks = getattr(mixer, "window", None), getattr(mixer, "sinks", None)
+    per_head = mixer.gate == "head"
+    gate = projected[:, mixer.q_rank + rank + rot:mixer.q_rank + rank + rot + mixer.gate_cols] if mixer.gate else None
+    # a gate of one number a head multiplies the attended latent (W_uv is linear: the head's output is gated all
+    # the same); a gate a value multiplies the head's output itself, in the last product
+    head_gate = gate if per_head else None
     q_latent = kernels.latent_prepare(
         projected, dq_at=0, q_rank=mixer.q_rank, q_weight=mixer.dq_norm_weight, dkv_at=mixer.q_rank, kv_rank=rank,
         kv_weight=mixer.dkv_norm_weight, rot_dim=rot, inv_freq=inv_freq, magnitude=magnitude,
-        positions=ctx.positions, slots=ctx.slots[group] if writes else None, key_cache=keys, eps=mixer.eps)
+        positions=ctx.positions, slots=ctx.slots[group] if writes else None, key_cache=keys, eps=mixer.eps,
+        pairing=pairing)
     from .linear import linear
 
     q = linear(q_latent, mixer.uq_weight).view(tokens, heads, mixer.key_dim + rot)
     folded = torch.empty((tokens, heads, rank + rot), dtype=projected.dtype, device=projected.device)
     kernels.head_product(q[:, :, :mixer.key_dim], mixer.uk_by_head, folded[:, :, :rank])
     if rot > 0:
-        kernels.rotate_heads(q[:, :, mixer.key_dim:], folded[:, :, rank:], inv_freq, magnitude, ctx.positions)
+        kernels.rotate_heads(q[:, :, mixer.key_dim:], folded[:, :, rank:], inv_freq, magnitude, ctx.positions, pairing)
     attended = None
     queries = folded.view(tokens, heads * (rank + rot))
     if (projected.dtype == torch.bfloat16 and TENSOR_CORE_WINDOWS and (ctx.decode_only or ctx.tile_row is not None)
@@ -393,21 +401,22 @@ def latent_attention(ctx, mixer, projected: torch.Tensor, run: int) -> torch.Ten
         # bfloat16: prompt portions in tiles of 64 tokens a head, single tokens one CTA a chunk of keys for all
         # heads at once (the cached rows are read once a token); the key tile in shared memory is the value tile
         attended = torch.empty((tokens, heads * rank), dtype=projected.dtype, device=projected.device)
-        sizes = dict(num_q=heads, num_kv=1, key_dim=rank + rot, value_dim=rank, window=None, keep_first=0,
-                     scale=mixer.scale)
+        sizes = dict(num_q=heads, num_kv=1, key_dim=rank + rot, value_dim=rank, window=window, keep_first=0,
+                     scale=mixer.scale, sinks=sinks, gate_per_head=per_head)
 
         def singles(part):
-            need = kernels.attention_tiles_singles_floats(part.stop - part.start, heads, rank, None, 0, ctx.max_context)
+            need = kernels.attention_tiles_singles_floats(part.stop - part.start, heads, rank, window, 0, ctx.max_context)
             kernels.attention_tiles_singles(
                 queries[part], keys, None, ctx.block_tables[group], ctx.positions[part], ctx.token_row[part], **sizes,
-                max_context=ctx.max_context, scratch=ctx.workspace(need), out=attended[part])
+                max_context=ctx.max_context, scratch=ctx.workspace(need), out=attended[part],
+                gate=None if head_gate is None else head_gate[part])
 
         if ctx.decode_only:
             singles(slice(0, tokens))
         else:
             if ctx.tile_row.shape[0] > 0:
                 kernels.attention_tiles(queries, keys, None, ctx.block_tables[group], ctx.positions, ctx.tile_row,
-                                        ctx.tile_first, ctx.tile_count, **sizes, out=attended)
+                                        ctx.tile_first, ctx.tile_count, **sizes, out=attended, gate=head_gate)
             for first, count in ctx.single_runs:
                 singles(slice(first, first + count))
     if attended is None:
@@ -416,11 +425,12 @@ def latent_attention(ctx, mixer, projected: torch.Tensor, run: int) -> torch.Ten
             scratch = ctx.workspace(kernels.attention_rows_scratch_floats(tokens, heads, rank, ctx.split_chunks))
         attended = kernels.attention_rows(
             queries, queries.stride(0), keys, None, ctx.block_tables[group], ctx.token_row, ctx.positions,
-            num_q=heads, num_kv=1, head_dim=rank + rot, value_dim=rank, value_offset=0, window=None,
-            scale=mixer.scale, scratch=scratch, max_chunks=ctx.split_chunks)
+            num_q=heads, num_kv=1, head_dim=rank + rot, value_dim=rank, value_offset=0, window=window,
+            scale=mixer.scale, scratch=scratch, max_chunks=ctx.split_chunks, sinks=sinks, gate=head_gate,
+            gate_per_head=per_head)
     gated = torch.empty((tokens, heads, mixer.value_dim), dtype=projected.dtype, device=projected.device)
-    gate = projected[:, mixer.q_rank + rank + rot:] if mixer.gate else None
-    kernels.head_product(attended.view(tokens, heads, rank), mixer.uv_by_head, gated, gate=gate)
+    kernels.head_product(attended.view(tokens, heads, rank), mixer.uv_by_head, gated,
+                         gate=gate if mixer.gate and not per_head else None)
     return gated.view(tokens, heads * mixer.value_dim)
 
 

@@ -429,6 +429,66 @@ def stream_norm(stream: torch.Tensor | None, weight: torch.Tensor | None, eps: f
     return y, stream_out
 
 
+def sandwich_norm(stream: torch.Tensor, y: torch.Tensor | None, *, post_weight: torch.Tensor | None = None,
+                  pre_weight: torch.Tensor | None = None, post_eps: float = 0.0, pre_eps: float = 0.0,
+                  row_scale: torch.Tensor | None = None, x: torch.Tensor | None = None,
+                  rows: torch.Tensor | None = None, out_dtype: torch.dtype | None = None):
+    """A norm behind a sublayer and the norm in front of the next, in one pass over a float32 residual stream.
+
+    t = y + row_scale[:, None] * x (the second term with ``row_scale`` float32 [tokens] and ``x`` [tokens, width]
+    of the storage type); s' = stream + t * rsqrt(mean(t^2) + post_eps) * post_weight, written back into
+    ``stream`` (without ``post_weight``: s' = stream + t; without ``y``: s' = stream); out = s' * rsqrt(mean(s'^2)
+    + pre_eps) * pre_weight, rounded once to ``out_dtype`` (without ``pre_weight`` no out).  All float32.
+    Returns (out, stream).  With ``rows`` (int32) only those rows of out are produced and nothing is written
+    back: (out, None)."""
+    _need_cuda(stream, y, post_weight, pre_weight, row_scale, x, rows)
+    if stream.dim() != 2 or stream.dtype != torch.float32 or not stream.is_contiguous():
+        raise KernelError("sandwich_norm wants a contiguous float32 [tokens, width] stream")
+    tokens, width = stream.shape
+    if y is not None and (y.shape != (tokens, width) or not y.is_contiguous()):
+        raise KernelError("sandwich_norm: y must match the stream")
+    if post_weight is not None and y is None:
+        raise KernelError("sandwich_norm: a norm behind the sublayer needs the sublayer's output")
+    weights = [w for w in (post_weight, pre_weight) if w is not None]
+    for w in weights:
+        if w.shape != (width,) or w.dtype != weights[0].dtype or not w.is_contiguous():
+            raise KernelError("sandwich_norm: norm weights are contiguous [width] of one dtype")
+    out_dtype = out_dtype or (weights[0].dtype if weights else torch.float32)
+    if (row_scale is None) != (x is None) or (x is not None and (
+            y is None or x.shape != (tokens, width) or x.dtype != out_dtype or not x.is_contiguous()
+            or row_scale.shape != (tokens,) or row_scale.dtype != torch.float32 or not row_scale.is_contiguous())):
+        raise KernelError("sandwich_norm: a scaled addend is float32 row_scale [tokens] and x [tokens, width] of "
+                          "the output's dtype, beside y")
+    if width * 4 > 200 * 1024:
+        raise KernelError(f"sandwich_norm: width {width} is larger than a row buffer of shared memory holds")
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelError("sandwich_norm: rows must be int32")
+    count = tokens if rows is None else rows.shape[0]
+    out = torch.empty((count, width), dtype=out_dtype, device=stream.device) if pre_weight is not None else None
+    fn = _fn("stream_norm", "tvb_sandwich_norm",
+             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+              c_void_p, c_int, c_int, c_float, c_float, c_int, c_void_p])
+    _check(fn(stream.data_ptr(), _ptr(y), dtype_tag(y.dtype) if y is not None else F32, _ptr(row_scale), _ptr(x),
+              _ptr(post_weight), _ptr(pre_weight), dtype_tag(weights[0].dtype) if weights else dtype_tag(out_dtype),
+              _ptr(out), dtype_tag(out_dtype), stream.data_ptr() if rows is None else None, _ptr(rows), count, width,
+              post_eps, pre_eps, _pdl("norm"), _stream()), "sandwich_norm")
+    return out, (stream if rows is None else None)
+
+
+def add_scaled_rows(y: torch.Tensor, x: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """y[t] += scale[t] * x[t] in place: contiguous float32 y [tokens, width], x of any storage type, float32
+    scale [tokens]."""
+    _need_cuda(y, x, scale)
+    if y.dim() != 2 or y.dtype != torch.float32 or not y.is_contiguous() or x.shape != y.shape \
+            or not x.is_contiguous() or scale.shape != (y.shape[0],) or scale.dtype != torch.float32 \
+            or not scale.is_contiguous():
+        raise KernelError("add_scaled_rows wants float32 y [tokens, width], x of its shape and float32 scale [tokens]")
+    fn = _fn("stream_norm", "tvb_add_scaled_rows", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(y.data_ptr(), x.data_ptr(), scale.data_ptr(), y.shape[0], y.shape[1], dtype_tag(x.dtype), _stream()),
+           "add_scaled_rows")
+    return y
+
+
 ACT_SILU, ACT_GELU_TANH = 0, 1
 ACTIVATIONS = {"silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
 
@@ -566,13 +626,17 @@ def projection_norm(proj: torch.Tensor, segments, positions: torch.Tensor | None
 def latent_prepare(proj: torch.Tensor, *, dq_at: int, q_rank: int, q_weight: torch.Tensor | None,
                    dkv_at: int, kv_rank: int, kv_weight: torch.Tensor, rot_dim: int,
                    inv_freq: torch.Tensor | None, magnitude: float, positions: torch.Tensor,
-                   slots: torch.Tensor | None, key_cache: torch.Tensor | None, eps: float) -> torch.Tensor | None:
+                   slots: torch.Tensor | None, key_cache: torch.Tensor | None, eps: float,
+                   pairing: str = "interleaved") -> torch.Tensor | None:
     """From a packed projection [tokens, columns] that holds a query latent (``q_rank`` columns from
     ``dq_at``) and a key/value latent with a part to rotate (``kv_rank + rot_dim`` columns from
     ``dkv_at``): returns RMSnorm(query latent) * q_weight [tokens, q_rank]; writes [RMSnorm(latent) *
     kv_weight | rotated part] to ``key_cache`` [pages, 1, page, kv_rank + rot_dim] at ``slots``.  The
-    pair (2i, 2i + 1) turns by position * inv_freq[i] (float32), cosine and sine times ``magnitude``."""
+    pair (2i, 2i + 1) (``pairing`` "half_split": (i, i + rot_dim / 2)) turns by position * inv_freq[i]
+    (float32), cosine and sine times ``magnitude``."""
     _need_cuda(proj, q_weight, kv_weight, inv_freq, positions, slots, key_cache)
+    if pairing not in PAIRINGS:
+        raise KernelError(f"latent_prepare: pairing {pairing!r} is not known")
     tokens = proj.shape[0]
     if proj.dim() != 2 or proj.stride(1) != 1 or min(dq_at, dkv_at) < 0 or \
             max(dq_at + q_rank, dkv_at + kv_rank + rot_dim) > proj.shape[1]:
@@ -594,11 +658,11 @@ def latent_prepare(proj: torch.Tensor, *, dq_at: int, q_rank: int, q_weight: tor
     q_latent = torch.empty((tokens, q_rank), dtype=proj.dtype, device=proj.device) if q_rank > 0 else None
     fn = _fn("latent_prepare", "tvb_latent_prepare",
              [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_int,
-              c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p])
+              c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p])
     _check(fn(proj.data_ptr(), proj.stride(0), dq_at, q_rank, _ptr(q_weight), _ptr(q_latent), q_rank, dkv_at,
               kv_rank, kv_weight.data_ptr(), dtype_tag(kv_weight.dtype), rot_dim, _ptr(inv_freq), magnitude,
               positions.data_ptr(), _ptr(slots), _ptr(key_cache) if slots is not None else None, eps, tokens,
-              dtype_tag(proj.dtype), _stream()), "latent_prepare")
+              dtype_tag(proj.dtype), PAIRINGS[pairing], _stream()), "latent_prepare")
     return q_latent
 
 
@@ -609,10 +673,13 @@ def _heads_view(t: torch.Tensor, heads: int, size: int, what: str) -> tuple[int,
 
 
 def rotate_heads(src: torch.Tensor, dst: torch.Tensor, inv_freq: torch.Tensor, magnitude: float,
-                 positions: torch.Tensor) -> None:
-    """dst[t, h, :] = src[t, h, :] with every pair (2i, 2i + 1) turned by position * inv_freq[i] and
-    cosine and sine multiplied by ``magnitude``; both [tokens, heads, rot_dim], any strides."""
+                 positions: torch.Tensor, pairing: str = "interleaved") -> None:
+    """dst[t, h, :] = src[t, h, :] with every pair (2i, 2i + 1) (``pairing`` "half_split": (i, i + rot_dim / 2))
+    turned by position * inv_freq[i] and cosine and sine multiplied by ``magnitude``; both [tokens, heads,
+    rot_dim], any strides."""
     _need_cuda(src, dst, inv_freq, positions)
+    if pairing not in PAIRINGS:
+        raise KernelError(f"rotate_heads: pairing {pairing!r} is not known")
     tokens, heads, rot_dim = src.shape
     s_strides = _heads_view(src, heads, rot_dim, "rotate_heads: src")
     d_strides = _heads_view(dst, heads, rot_dim, "rotate_heads: dst")
@@ -621,9 +688,10 @@ def rotate_heads(src: torch.Tensor, dst: torch.Tensor, inv_freq: torch.Tensor, m
         raise KernelError("rotate_heads: equal shapes, float32 inv_freq [rot_dim / 2], int32 positions [tokens]")
     fn = _fn("latent_prepare", "tvb_rotate_heads",
              [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_int, c_int, c_void_p, c_float,
-              c_void_p, c_int, c_int, c_void_p])
+              c_void_p, c_int, c_int, c_int, c_void_p])
     _check(fn(src.data_ptr(), *s_strides, dst.data_ptr(), *d_strides, heads, rot_dim, inv_freq.data_ptr(),
-              magnitude, positions.data_ptr(), tokens, dtype_tag(src.dtype), _stream()), "rotate_heads")
+              magnitude, positions.data_ptr(), tokens, dtype_tag(src.dtype), PAIRINGS[pairing], _stream()),
+           "rotate_heads")
 
 
 HEAD_PRODUCT_MAX_K = 1536        # eight float32 rows of x wait in 48 KB of shared memory
@@ -745,10 +813,59 @@ def route_gated_act(logits: torch.Tensor, proj: torch.Tensor, *, experts: int, t
     return out
 
 
+def route_softmax_gated(logits: torch.Tensor, proj: torch.Tensor, *, experts: int, identity: int, top: int, ff: int,
+                        correction: torch.Tensor | None = None, renormalise: bool = False,
+                        out: torch.Tensor | None = None, weights_out: torch.Tensor | None = None):
+    """Softmax routing over experts and pass-through slots, and gated experts, between the packed input and
+    output products.
+
+    ``logits`` float32 [tokens, experts + identity]; the scores are their softmax over all slots, the ``top``
+    slots with the largest score + ``correction`` (float32 [experts + identity]) are chosen, and a chosen
+    slot's weight is its score (``renormalise``: over the sum of the chosen scores).  ``proj`` [tokens, 2 *
+    experts * ff] holds [gate | up] of every expert; the result [tokens, experts * ff] holds silu(gate) * up
+    times the expert's weight (0 if not chosen).  The last ``identity`` slots have no columns: the sum of their
+    weights comes back as float32 [tokens] (None without such slots), and the caller adds that many times the
+    experts' input to the down-projection's result.  Returns (inner, identity weights)."""
+    _need_cuda(logits, proj, correction, out, weights_out)
+    tokens = proj.shape[0]
+    slots = experts + identity
+    columns = experts * ff
+    if logits.dtype != torch.float32 or logits.shape != (tokens, slots) or logits.stride(1) != 1:
+        raise KernelError("route_softmax_gated: router logits are float32 [tokens, experts + identity]")
+    if proj.dim() != 2 or proj.shape[1] != 2 * columns or proj.stride(1) != 1 or experts <= 0 or identity < 0 \
+            or slots > ROUTE_MAX_EXPERTS or top <= 0:
+        raise KernelError("route_softmax_gated: the projection must be [tokens, 2 * experts * ff]")
+    if correction is not None and (correction.dtype != torch.float32 or correction.shape != (slots,)
+                                   or not correction.is_contiguous()):
+        raise KernelError("route_softmax_gated: the correction is contiguous float32 [experts + identity]")
+    if out is None:
+        out = torch.empty((tokens, columns), dtype=proj.dtype, device=proj.device)
+    elif out.shape != (tokens, columns) or out.dtype != proj.dtype or out.stride(1) != 1:
+        raise KernelError("route_softmax_gated: out must be [tokens, experts * ff] of the projection's dtype")
+    if weights_out is not None and (weights_out.dtype != torch.float32 or weights_out.shape != (tokens, slots)
+                                    or not weights_out.is_contiguous()):
+        raise KernelError("route_softmax_gated: weights_out must be contiguous float32 [tokens, experts + identity]")
+    passed = torch.empty((tokens,), dtype=torch.float32, device=proj.device) if identity else None
+    fn = _fn("routed_act", "tvb_route_softmax_gated",
+             [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_int,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(logits.data_ptr(), logits.stride(0), _ptr(correction), proj.data_ptr(), proj.stride(0),
+              out.data_ptr(), out.stride(0), _ptr(weights_out), _ptr(passed), tokens, experts, identity, top,
+              1 if renormalise else 0, ff, dtype_tag(proj.dtype), _stream()), "route_softmax_gated")
+    return out, passed
+
+
 # --------------------------------------------------- retention: linear attention with a decay a head
 RETENTION_MAX_DIM = 256
 RETENTION_ACTS = {None: 0, "silu": 1, "sigmoid": 2}
 SM_COUNT = 148                    # a B200's SMs: what the choice of a piece's size fills
+
+
+_RETENTION_SCAN_ARGS = [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                        c_void_p, c_void_p]
+_RETENTION_FINISH_ARGS = [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_float,
+                          c_int, c_void_p, c_int, c_void_p]
 
 
 def retention_lanes(dim: int) -> int:
@@ -843,20 +960,105 @@ def retention(proj: torch.Tensor, *, q_at: int, k_at: int, v_at: int, g_at: int 
     _check(prepare(proj.data_ptr(), proj.stride(0), q_at, k_at, heads, dim, _ptr(inv_freq), rot_dims,
                    PAIRINGS[pairing], key_scale, positions.data_ptr(), turned[0].data_ptr(), turned[1].data_ptr(),
                    tokens, tag, _stream()), "retention_prepare")
-    scan = _fn("retention", "tvb_retention_scan",
-               [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    scan = _fn_of("retention", "tvb_retention_scan", _RETENTION_SCAN_ARGS)
     _check(scan(turned[0].data_ptr(), turned[1].data_ptr(), proj.data_ptr() + v_at * proj.element_size(),
                 proj.stride(0), state.data_ptr(), decay.data_ptr(), row_starts.data_ptr(), state_slots.data_ptr(),
                 token_row.data_ptr(), raw_out.data_ptr(), rows, heads, dim, vdim, lanes, _ptr(parts), segment, pieces, tag,
-                _stream()), "retention_scan", launches=3 if segment else 1)
-    finish = _fn("retention", "tvb_retention_finish",
-                 [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_float, c_int,
-                  c_int, c_void_p])
+                None, None, None, _stream()), "retention_scan", launches=3 if segment else 1)
+    finish = _fn_of("retention", "tvb_retention_finish", _RETENTION_FINISH_ARGS)
     gate_ptr = None if g_at is None else proj.data_ptr() + g_at * proj.element_size()
     _check(finish(raw_out.data_ptr(), gate_ptr, proj.stride(0), out.data_ptr(), out.stride(0), tokens, heads, vdim,
-                  1 if unit_norm else 0, eps, RETENTION_ACTS[gate_act if g_at is not None else None], tag,
+                  1 if unit_norm else 0, eps, RETENTION_ACTS[gate_act if g_at is not None else None], None, tag,
                   _stream()), "retention_finish")
+    return out
+
+
+GATED_QUERY_ACTS = {None: 0, "silu": 1}
+
+
+def gated_recurrence(proj: torch.Tensor, *, q_at: int, g_at: int, v_at: int, heads: int, dim: int, vdim: int,
+                     state: torch.Tensor, row_starts: torch.Tensor, state_slots: torch.Tensor,
+                     token_row: torch.Tensor, bias: torch.Tensor | None = None, lower: torch.Tensor | None = None,
+                     query_act: str | None = "silu", k_at: int | None = None, unit_norm: bool = True,
+                     norm_weight: torch.Tensor | None = None, eps: float = 0.0, out: torch.Tensor | None = None,
+                     raw_out: torch.Tensor | None = None, lanes: int = 0, segment: int | None = None) -> torch.Tensor:
+    """A linear recurrence whose decay is a gate a token and key channel, between a mixer's packed input
+    projection and its output projection.
+
+    ``proj`` [tokens, columns] holds q heads (``dim`` wide) from column ``q_at``, the gates' pre-activations
+    (heads of ``dim``) from ``g_at`` and v heads (``vdim``) from ``v_at``.  q = act(q) (``query_act``: None or
+    "silu"); g = lower + (1 - lower) * sigmoid(pre-activation + bias) with float32 ``bias`` and ``lower``
+    [heads * dim] (either may be None: 0).  Per request and head, token by token, S <- diag(g) S + k v^T and
+    o = S^T q from the float32 ``state`` [slots, heads, dim, vdim] of the request's slot, which is left as the
+    state after the step's last token.  The keys are what the gate lets go, k = 1 - g, unless ``k_at`` names
+    columns with keys of their own.  Every head's o is divided by its root mean square (``unit_norm``, with
+    ``eps``) and multiplied by ``norm_weight`` (float32 [vdim], one for all heads), then rounded to the
+    projection's type: [tokens, heads * vdim].  Gates, products, state and sums are float32.
+
+    ``segment`` as in :func:`retention`: 0 walks whole entries, n > 0 cuts them into pieces of n tokens that
+    run side by side (a piece's decay is the product of its gates, channel by channel), None chooses."""
+    _need_cuda(proj, state, row_starts, state_slots, token_row, bias, lower, norm_weight, out, raw_out)
+    tokens = proj.shape[0]
+    rows = state_slots.shape[0]
+    per = heads * dim
+    if proj.dim() != 2 or proj.stride(1) != 1:
+        raise KernelError("gated_recurrence: the projection must be [tokens, columns] with contiguous rows")
+    ends = [q_at + per, g_at + per, v_at + heads * vdim] + ([] if k_at is None else [k_at + per])
+    if min(q_at, g_at, v_at, 0 if k_at is None else k_at) < 0 or max(ends) > proj.shape[1]:
+        raise KernelError("gated_recurrence: the heads do not fit the projection's rows")
+    if not 0 < dim <= RETENTION_MAX_DIM or vdim <= 0:
+        raise KernelError(f"gated_recurrence takes key sizes up to {RETENTION_MAX_DIM}, not {dim}")
+    if state.dtype != torch.float32 or state.dim() != 4 or state.shape[1:] != (heads, dim, vdim) \
+            or not state.is_contiguous():
+        raise KernelError("gated_recurrence: the state is contiguous float32 [slots, heads, dim, vdim]")
+    for name, t, shape in (("row_starts", row_starts, (rows + 1,)), ("state_slots", state_slots, (rows,)),
+                           ("token_row", token_row, (tokens,))):
+        if t.dtype != torch.int32 or t.shape != shape or not t.is_contiguous():
+            raise KernelError(f"gated_recurrence: {name} must be contiguous int32 {list(shape)}")
+    for name, t, shape in (("bias", bias, (per,)), ("lower", lower, (per,)), ("norm_weight", norm_weight, (vdim,))):
+        if t is not None and (t.dtype != torch.float32 or t.shape != shape or not t.is_contiguous()):
+            raise KernelError(f"gated_recurrence: {name} must be contiguous float32 {list(shape)}")
+    if query_act not in GATED_QUERY_ACTS:
+        raise KernelError(f"gated_recurrence: the queries' activation is None or 'silu', not {query_act!r}")
+    if out is None:
+        out = torch.empty((tokens, heads * vdim), dtype=proj.dtype, device=proj.device)
+    elif out.shape != (tokens, heads * vdim) or out.dtype != proj.dtype or out.stride(1) != 1:
+        raise KernelError("gated_recurrence: out must be [tokens, heads * vdim] of the projection's dtype")
+    if raw_out is None:
+        raw_out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=proj.device)
+    elif raw_out.shape != (tokens, heads * vdim) or raw_out.dtype != torch.float32 or not raw_out.is_contiguous():
+        raise KernelError("gated_recurrence: raw_out must be contiguous float32 [tokens, heads * vdim]")
+    if segment is None:
+        segment = retention_segment(tokens, rows, heads, dim, vdim)
+    if segment < 0:
+        raise KernelError("gated_recurrence: a piece has at least one token")
+    from .build import variant
+    library = variant("retention", RET_GATED=1 if k_at is None else 2)
+    pieces = tokens // segment + rows if segment else 0
+    # float32 rows: q, gates, (keys), and for pieces the queries times the running products of the gates
+    work = torch.empty((4, tokens, per), dtype=torch.float32, device=proj.device)
+    parts = torch.empty((pieces, heads, dim, vdim), dtype=torch.float32, device=proj.device) if segment else None
+    piece_gates = torch.empty((pieces, heads, dim), dtype=torch.float32, device=proj.device) if segment else None
+    tag = dtype_tag(proj.dtype)
+    prepare = _fn_of(library, "tvb_gated_prepare",
+                     [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                      c_int, c_void_p])
+    _check(prepare(proj.data_ptr(), proj.stride(0), q_at, g_at, per, _ptr(bias), _ptr(lower),
+                   GATED_QUERY_ACTS[query_act], work[0].data_ptr(), work[1].data_ptr(), tokens, tag, _stream()),
+           "gated_prepare")
+    keys = None
+    if k_at is not None:
+        keys = work[2]
+        keys.copy_(proj[:, k_at:k_at + per])
+    scan = _fn_of(library, "tvb_retention_scan", _RETENTION_SCAN_ARGS)
+    _check(scan(work[0].data_ptr(), _ptr(keys), proj.data_ptr() + v_at * proj.element_size(), proj.stride(0),
+                state.data_ptr(), None, row_starts.data_ptr(), state_slots.data_ptr(), token_row.data_ptr(),
+                raw_out.data_ptr(), rows, heads, dim, vdim, lanes, _ptr(parts), segment, pieces, tag,
+                work[1].data_ptr(), work[3].data_ptr() if segment else None, _ptr(piece_gates), _stream()),
+           "gated_recurrence_scan", launches=4 if segment else 1)
+    finish = _fn_of(library, "tvb_retention_finish", _RETENTION_FINISH_ARGS)
+    _check(finish(raw_out.data_ptr(), None, proj.stride(0), out.data_ptr(), out.stride(0), tokens, heads, vdim,
+                  1 if unit_norm else 0, eps, 0, _ptr(norm_weight), tag, _stream()), "gated_recurrence_finish")
     return out
 
 

@@ -345,7 +345,10 @@ class LatentAttention(Part):
     (weight ``dkv.norm``), are the latent c, the rest one rotated key part that all heads share.  A
     head's plain key is W_uk c and its value W_uv c; the score is (q_plain . k_plain + q_rot . k_rot) *
     scale, softmax over the causal keys.  The concatenated heads are multiplied by sigmoid(W_g x)
-    (``gate``) and projected by W_o.
+    (``gate``) and projected by W_o.  ``window``: query i sees the keys j with 0 <= i - j < window.  ``sink``: a
+    learned number a head (tensor ``sink``) whose exponential is added to the softmax's denominator and to
+    nothing else.  ``gate="head"``: the gate is one number a head, sigmoid(W_g x)_h with W_g [heads, width].  The
+    rotated part turns as neighbouring pairs or as pairs of its two halves, as the position part says.
 
     Only [c | rotated key part] is cached, as one key row a token of one kv head.  The up-projections
     never touch the cache: W_uk is folded into the query (q_plain^T W_uk is a query over c itself,
@@ -355,7 +358,12 @@ class LatentAttention(Part):
 
     def __init__(self, ctx: BuildContext, *, hidden_size: int, num_heads: int, key_dim: int, rot_dim: int,
                  value_dim: int, q_rank: int, kv_rank: int, scale: float, eps: float, position=None,
-                 gate: bool = True, float32_output: bool = False, names: dict | None = None) -> None:
+                 gate: bool | str = True, float32_output: bool = False, names: dict | None = None,
+                 window: int | None = None, sink: bool = False) -> None:
+        if gate not in (False, True, "head"):
+            raise ValueError(f"gate is False, True or 'head', not {gate!r}")
+        if window is not None and window <= 0:
+            raise ValueError("a window holds at least one key")
         if rot_dim % 2:
             raise ValueError("the rotated part of a head has an even size")
         if (rot_dim > 0) != (position is not None):
@@ -367,15 +375,18 @@ class LatentAttention(Part):
         self.key_dim, self.rot_dim, self.value_dim = key_dim, rot_dim, value_dim
         self.q_rank, self.kv_rank = q_rank, kv_rank
         self.scale, self.eps = float(scale), float(eps)
-        self.gate = bool(gate)
+        self.gate = gate
+        self.window, self.has_sink = window, bool(sink)
+        self.sink = self.sinks = None
         self.out_dtype = torch.float32 if float32_output else None
         n = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk",
-             "uv": "uv", "g": "g", "o": "o", **(names or {})}
+             "uv": "uv", "g": "g", "o": "o", "sink": "sink", **(names or {})}
         self.names = {key: f"{ctx.prefix}.{value}" for key, value in n.items()}
         self.position = ctx.build("position", position, ctx) if position is not None else None
-        if self.position is not None and (getattr(self.position, "pairing", None) != "interleaved"
+        if self.position is not None and (getattr(self.position, "pairing", None) not in ("interleaved", "half_split")
+                                          or not hasattr(self.position, "inv_freq")
                                           or self.position.rot_dims != rot_dim):
-            raise ValueError("the rotated part is turned as neighbouring pairs over its whole size")
+            raise ValueError("the rotated part is turned over its whole size, by position * frequency")
         self.in_weight = self.uq_weight = self.uk_weight = self.uv_weight = self.o_weight = None
         self.dq_norm_weight = self.dkv_norm_weight = None
         self.uk_by_head = self.uv_by_head = None
@@ -389,11 +400,16 @@ class LatentAttention(Part):
         """Size of a cached row: the latent and the rotated key part."""
         return self.kv_rank + self.rot_dim
 
+    @property
+    def gate_cols(self) -> int:
+        return 0 if not self.gate else self.num_heads if self.gate == "head" else self.out_cols
+
     def param_specs(self):
         rows = [(self.names["dq"], self.q_rank), (self.names["dkv"], self.row_dim)]
         if self.gate:
-            rows.append((self.names["g"], self.out_cols))
-        return [
+            rows.append((self.names["g"], self.gate_cols))
+        sink = [ParamSpec.single("sink", self.names["sink"], (self.num_heads,), role="vector")] if self.has_sink else []
+        return sink + [
             ParamSpec.packed("in_weight", rows, self.hidden_size),
             ParamSpec.single("dq_norm_weight", self.names["dq_norm"], (self.q_rank,), role="vector", init="around_one"),
             ParamSpec.single("dkv_norm_weight", self.names["dkv_norm"], (self.kv_rank,), role="vector",
@@ -412,12 +428,14 @@ class LatentAttention(Part):
         ([heads, kv_rank, key_dim]: the product with it folds W_uk into the query), W_uv as it is."""
         self.uk_by_head = self.uk_weight.view(self.num_heads, self.key_dim, self.kv_rank).transpose(1, 2).contiguous()
         self.uv_by_head = self.uv_weight.view(self.num_heads, self.value_dim, self.kv_rank)
+        if self.has_sink and self.sink is not None:
+            self.sinks = self.sink.to(torch.float32).contiguous()
 
     def streamed_weights(self):
         return [self.in_weight, self.uq_weight, self.o_weight]
 
     def cache_need(self):
-        return KVNeed(1, self.row_dim, None, self.kv_rank, 0, value_offset=0)
+        return KVNeed(1, self.row_dim, self.window, self.kv_rank, 0, value_offset=0)
 
     def takes_tensor_memory_tiles(self, page_size: int) -> bool:
         return False
@@ -425,7 +443,7 @@ class LatentAttention(Part):
     def scratch_floats(self, rows: int, chunks: int) -> int:
         span = chunks * kernels.attention_chunk_keys()
         return max(kernels.attention_rows_scratch_floats(rows, self.num_heads, self.kv_rank, chunks),
-                   kernels.attention_tiles_singles_floats(rows, self.num_heads, self.kv_rank, None, 0, span))
+                   kernels.attention_tiles_singles_floats(rows, self.num_heads, self.kv_rank, self.window, 0, span))
 
     def forward(self, x, ctx, run: int):
         projected = linear(x, self.in_weight)

@@ -180,6 +180,64 @@ class PostNormResidualBlock(Block):
         return None, stream
 
 
+class SandwichResidualBlock(Block):
+    """A norm before and a norm behind every sublayer: x <- x + post1(mixer(pre1(x))), then, where the layer has a
+    feed-forward, x <- x + post2(feed_forward(pre2(x))).  The stream x is float32 whatever the storage type.
+
+    A norm behind a sublayer and the norm in front of the next run as one kernel (``norm.after``); what the
+    block's last sublayer leaves is handed on as ``stream.pending`` (:class:`parts.norm.PendingUpdate`), which
+    the next block's first norm, or the model's last norm, adds in its own pass.  A feed-forward that offers
+    ``forward_carried(x, ctx) -> (y, row_scale)`` stands for y + row_scale[:, None] * x (experts that hand
+    their input on): the scaled term joins inside the norm kernel.  The block returns (None, stream)."""
+
+    def __init__(self, ctx: BuildContext, *, mixer, feed_forward, norm, mixer_norm_name: str,
+                 mixer_post_norm_name: str, feed_forward_norm_name: str, feed_forward_post_norm_name: str,
+                 mixer_name: str, feed_forward_name: str) -> None:
+        def build_norm(name):
+            return ctx.build("norm", norm.with_params(name=f"{ctx.prefix}.{name}"), ctx)
+
+        self.mixer_norm, self.mixer_post_norm = build_norm(mixer_norm_name), build_norm(mixer_post_norm_name)
+        self.mixer = ctx.build("mixer", mixer, ctx.child(mixer_name))
+        self.feed_forward_norm = self.feed_forward_post_norm = self.feed_forward = None
+        if feed_forward is not None:
+            self.feed_forward_norm = build_norm(feed_forward_norm_name)
+            self.feed_forward_post_norm = build_norm(feed_forward_post_norm_name)
+            self.feed_forward = ctx.build("feed_forward", feed_forward, ctx.child(feed_forward_name))
+        for part in (self.mixer_norm, self.mixer_post_norm):
+            if not hasattr(part, "after") or not hasattr(part, "resume"):
+                raise ValueError("a sandwich block needs norms over a float32 stream that offer after() and resume()")
+
+    def children(self):
+        return [part for part in (self.mixer_norm, self.mixer_post_norm, self.mixer, self.feed_forward_norm,
+                                  self.feed_forward_post_norm, self.feed_forward) if part is not None]
+
+    def forward(self, hidden, residual, ctx, run: int):
+        from .norm import PendingUpdate
+
+        if residual is None:                 # the first block: the embedding starts the stream
+            x, stream = self.mixer_norm.add(hidden, None)
+        else:
+            if hidden is not None:
+                raise ValueError("a sandwich block follows blocks that leave nothing but the stream")
+            stream = residual
+            if getattr(stream, "pending", None) is not None:
+                x, _ = self.mixer_norm.resume(stream)
+            else:
+                x = self.mixer_norm.forward(stream)
+        mixed = self.mixer.forward(x, ctx, run)
+        if self.feed_forward is None:
+            stream.pending = PendingUpdate(mixed, self.mixer_post_norm)
+            return None, stream
+        x, stream = self.mixer_post_norm.after(stream, mixed, self.feed_forward_norm)
+        if hasattr(self.feed_forward, "forward_carried"):
+            y, row_scale = self.feed_forward.forward_carried(x, ctx)
+            stream.pending = PendingUpdate(y, self.feed_forward_post_norm, row_scale, x if row_scale is not None else None)
+        else:
+            stream.pending = PendingUpdate(self.feed_forward.forward(x, ctx), self.feed_forward_post_norm)
+        return None, stream
+
+
 register_part("block", "prenorm_residual", PreNormResidualBlock)
+register_part("block", "sandwich_residual", SandwichResidualBlock)
 register_part("block", "postnorm_residual", PostNormResidualBlock)
 register_part("block", "parallel_residual", ParallelResidualBlock)

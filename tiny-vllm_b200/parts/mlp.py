@@ -219,3 +219,76 @@ class GatedRoutedExperts(Part):
 
 
 register_part("feed_forward", "gated_routed_experts", GatedRoutedExperts)
+
+
+class SoftmaxRoutedExperts(Part):
+    """A mixture of gated experts, down_e(silu(gate_e h) * (up_e h)), routed by a softmax over all slots, some of
+    which may hand their input on unchanged.
+
+    Router logits z = W_router h are float32 and have ``experts + identity`` entries; the scores are s =
+    softmax(z) over all of them.  A token uses the ``top`` slots with the largest choice scores s + correction
+    (tensor ``correction``, with ``correction=True``; the weights use s without it), weighted by s as it is
+    (``renormalise``: divided by the sum of the chosen scores).  The last ``identity`` slots are experts without
+    tensors whose output is h itself.
+
+    As in :class:`RoutedExperts` the experts are two products: [gate_e | up_e] of all experts are the rows of
+    one weight, the down-projections stand side by side in another, and one kernel between the two routes,
+    activates and weights (exactly 0 for experts not chosen).  The pass-through slots cost one number a token:
+    the sum of their weights, times which h is added (``forward``), or which a norm kernel behind the part adds
+    for it (``forward_carried``)."""
+
+    def __init__(self, ctx: BuildContext, *, hidden_size: int, experts: int, top: int, ff: int, identity: int = 0,
+                 correction: bool = False, renormalise: bool = False, float32_output: bool = False,
+                 names: dict | None = None) -> None:
+        if experts <= 0 or identity < 0 or experts + identity > kernels.ROUTE_MAX_EXPERTS or not 0 < top <= experts + identity:
+            raise ValueError(f"a token uses between 1 and all of at most {kernels.ROUTE_MAX_EXPERTS} slots")
+        self.hidden_size, self.experts, self.identity, self.top, self.ff = hidden_size, experts, identity, top, ff
+        self.has_correction, self.renormalise = bool(correction), bool(renormalise)
+        self.out_dtype = torch.float32 if float32_output else None
+        n = {"router": "router", "correction": "correction", "expert": "e{index}", "gate": "gate", "up": "up",
+             "down": "down", **(names or {})}
+        self.router_name = f"{ctx.prefix}.{n['router']}"
+        self.correction_name = f"{ctx.prefix}.{n['correction']}"
+        stems = [f"{ctx.prefix}.{n['expert'].format(index=index)}" for index in range(experts)]
+        self.in_sources = [(f"{stem}.{n[which]}", ff) for stem in stems for which in ("gate", "up")]
+        self.down_sources = [(f"{stem}.{n['down']}", ff) for stem in stems]
+        self.router_weight = self.in_weight = self.down_weight = self.correction = None
+
+    @property
+    def slots(self) -> int:
+        return self.experts + self.identity
+
+    def param_specs(self):
+        specs = [ParamSpec.single("router_weight", self.router_name, (self.slots, self.hidden_size)),
+                 ParamSpec.packed("in_weight", self.in_sources, self.hidden_size),
+                 ParamSpec.side_by_side("down_weight", self.hidden_size, self.down_sources)]
+        if self.has_correction:
+            specs.append(ParamSpec.single("correction", self.correction_name, (self.slots,), role="vector"))
+        return specs
+
+    def finalize(self) -> None:
+        if self.correction is not None:
+            self.correction = self.correction.to(torch.float32).contiguous()
+
+    def streamed_weights(self):
+        return [self.in_weight, self.down_weight]
+
+    def forward_carried(self, x, ctx):
+        """(y, row_scale): the part's output is y + row_scale[:, None] * x; ``row_scale`` (float32 [tokens], the
+        weights of the chosen pass-through slots) is None where the part has no such slots."""
+        logits = linear(x, self.router_weight, out_dtype=torch.float32)
+        inner, passed = kernels.route_softmax_gated(
+            logits, linear(x, self.in_weight), experts=self.experts, identity=self.identity, top=self.top,
+            ff=self.ff, correction=self.correction, renormalise=self.renormalise)
+        return linear(inner, self.down_weight, out_dtype=self.out_dtype), passed
+
+    def forward(self, x, ctx):
+        y, passed = self.forward_carried(x, ctx)
+        if passed is None:
+            return y
+        if y.dtype != torch.float32:
+            raise kernels.KernelError("experts that hand their input on leave a float32 result (float32_output)")
+        return kernels.add_scaled_rows(y, x, passed)
+
+
+register_part("feed_forward", "softmax_routed_experts", SoftmaxRoutedExperts)

@@ -39,6 +39,17 @@ class RMSNorm(Part):
         return kernels.rms_norm(x, self.weight, self.eps, residual=residual, rows=rows)
 
 
+class PendingUpdate:
+    """What a block left for the next norm to add to the float32 stream: norm(y + row_scale * x), with ``norm`` a
+    :class:`StreamRMSNorm` (or None: y + row_scale * x as it is) and the scaled term optional.  It rides on the
+    stream tensor as ``stream.pending``; whoever norms the stream next adds it in the same pass."""
+
+    __slots__ = ("y", "norm", "row_scale", "x")
+
+    def __init__(self, y, norm=None, row_scale=None, x=None) -> None:
+        self.y, self.norm, self.row_scale, self.x = y, norm, row_scale, x
+
+
 class StreamRMSNorm(Part):
     """RMSNorm in front of a float32 residual stream: y = s * rsqrt(mean(s^2) + eps) * weight with
     statistics, scaling and the product with the weight in float32 and one rounding, to the
@@ -72,9 +83,34 @@ class StreamRMSNorm(Part):
 
     def forward(self, x):
         """norm(x) for a float32 stream or for activations that start one."""
+        if getattr(x, "pending", None) is not None:
+            return self.resume(x)[0]
         if x.dtype == torch.float32:
             return kernels.stream_norm(x, self.weight, self.eps, out_dtype=self.out_dtype)[0]
         return kernels.stream_norm(None, self.weight, self.eps, add=x, out_dtype=self.out_dtype)[0]
+
+    def resume(self, stream, rows=None):
+        """(norm(s'), s') with s' = stream + what the block before left pending on it (:class:`PendingUpdate`:
+        a sublayer's output with a norm of its own behind it), in one pass; the stream is updated in place and
+        nothing is pending afterwards.  With ``rows`` only those rows of the result, and nothing is written."""
+        pending = stream.pending
+        post = pending.norm
+        out, updated = kernels.sandwich_norm(
+            stream, pending.y, post_weight=None if post is None else post.weight,
+            post_eps=0.0 if post is None else post.eps, pre_weight=self.weight, pre_eps=self.eps,
+            row_scale=pending.row_scale, x=pending.x, rows=rows, out_dtype=self.out_dtype)
+        if rows is None:
+            stream.pending = None
+        return out, updated
+
+    def after(self, stream, y, following=None, row_scale=None, x=None):
+        """This norm behind a sublayer: (following(s'), s') with s' = stream + norm(y + row_scale * x), the stream
+        updated in place; ``following`` is the norm in front of the next sublayer (None: no first result)."""
+        return kernels.sandwich_norm(
+            stream, y, post_weight=self.weight, post_eps=self.eps,
+            pre_weight=None if following is None else following.weight,
+            pre_eps=0.0 if following is None else following.eps, row_scale=row_scale, x=x,
+            out_dtype=self.out_dtype)
 
     def add(self, x, residual):
         """(norm(residual + x), residual + x); without a residual x starts the stream, without x
@@ -87,6 +123,8 @@ class StreamRMSNorm(Part):
         """norm(residual + x) on the rows named by ``rows`` only; nothing is written back."""
         if residual is None and x.dtype == torch.float32:
             x, residual = None, x
+        if x is None and getattr(residual, "pending", None) is not None:
+            return self.resume(residual, rows=rows)[0]
         return kernels.stream_norm(residual, self.weight, self.eps, add=x, rows=rows,
                                    out_dtype=self.out_dtype)[0]
 

@@ -59,7 +59,12 @@ class RopeInterleaved(Part):
     beyond ``original`` positions: with d(t) = dims * ln(original / (2 pi t)) / (2 ln base), lo =
     max(floor(d(fast)), 0), hi = min(ceil(d(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo,
     0.001), 0, 1), pair i turns at f_i / factor * ramp_i + f_i * (1 - ramp_i), and cosine and sine are
-    multiplied by ``magnitude`` = 0.1 ln(factor) + 1 (1 without scaling)."""
+    multiplied by ``magnitude`` = 0.1 ln(factor) + 1 (1 without scaling).
+
+    A ``scaling`` of (``factor``, ``low``, ``high``, ``original``) is another rule, by wavelength: with l_i = 2 pi /
+    f_i, a pair whose wave is shorter than original / high keeps f_i, one whose wave is longer than original /
+    low turns at f_i / factor, and between the two, with s = (original / l_i - low) / (high - low), at
+    (1 - s) f_i / factor + s f_i; cosine and sine keep their size."""
 
     pairing = "interleaved"
 
@@ -70,13 +75,19 @@ class RopeInterleaved(Part):
         self.base = float(base)
         self.scaling = dict(scaling) if scaling else None
         self.magnitude = 1.0
+        self.by_wavelength = self.scaling is not None and "low" in self.scaling
         if self.scaling is not None:
-            missing = [key for key in ("factor", "original", "fast", "slow") if key not in self.scaling]
+            wanted = ("factor", "original", "low", "high") if self.by_wavelength else ("factor", "original", "fast", "slow")
+            missing = [key for key in wanted if key not in self.scaling]
             if missing:
                 raise ValueError("rotary scaling lacks " + ", ".join(missing))
             if not self.scaling["factor"] > 0:
                 raise ValueError("the scaling factor must be positive")
-            self.magnitude = 0.1 * math.log(float(self.scaling["factor"])) + 1.0
+            if self.by_wavelength:
+                if not self.scaling["high"] > self.scaling["low"] > 0 or not self.scaling["original"] > 0:
+                    raise ValueError("rotary scaling by wavelength wants 0 < low < high and a positive original length")
+            else:
+                self.magnitude = 0.1 * math.log(float(self.scaling["factor"])) + 1.0
         self.device = ctx.device
         self.inv_freq = None
 
@@ -84,7 +95,14 @@ class RopeInterleaved(Part):
         """The pairs' frequencies, evaluated in double precision and rounded to float32 once."""
         exponent = torch.arange(0, self.rot_dims, 2, dtype=torch.float64) / self.rot_dims
         freqs = self.base ** -exponent
-        if self.scaling is not None:
+        if self.by_wavelength:
+            factor, original = float(self.scaling["factor"]), float(self.scaling["original"])
+            low, high = float(self.scaling["low"]), float(self.scaling["high"])
+            wave = 2.0 * math.pi / freqs
+            blend = ((original / wave - low) / (high - low)).clamp(0.0, 1.0)
+            blended = (1.0 - blend) * freqs / factor + blend * freqs
+            freqs = torch.where(wave < original / high, freqs, torch.where(wave > original / low, freqs / factor, blended))
+        elif self.scaling is not None:
             factor, original = float(self.scaling["factor"]), float(self.scaling["original"])
 
             def dimension(turns: float) -> float:
