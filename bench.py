@@ -1276,6 +1276,198 @@ def bimolix_workload(args) -> int:
     return 0
 
 
+# ------------------------------------------- Fezavik beside Bimolix at equal layer sizes
+FEZAVIK_WINDOW, FEZAVIK_IDENTITY = 1024, 2
+# (kernel of the new design, its counterpart in Bimolix) by what they do
+FEZAVIK_LIKE = (
+    ("sandwich_norm", "stream_norm", "norm(s) around the residual sum"),
+    ("projection_norm + qkv_prepare", "qkv_prepare", "q/k norm, rotation, cache write"),
+    ("attention_tiles[attention]", "attention_tiles", "prompt attention"),
+    ("attention_tiles_singles[attention]", "attention_tiles_singles", "decode attention"),
+    ("attention_tiles[latent] / attention_tiles_singles[latent]", "attention_tiles / attention_tiles_singles",
+     "attention over latent rows"),
+    ("gated_recurrence", "retention", "the recurrent mixer"),
+    ("route_softmax_gated", "route_gated_act", "routing + activation"),
+)
+
+
+def fezavik_config(size: str, layers: int):
+    """Attention, recurrent and latent layers in turn, all with experts as many and as wide as Bimolix's at
+    this size plus pass-through slots; windows of 1,024 keys."""
+    from tinyvllm_b200.models import FezavikConfig
+    from tinyvllm_b200.models.fezavik import FezavikExperts, FezavikLayer, FezavikRotation
+
+    width, heads, kv, dim, ff = KELASUN_SIZES[size]
+    q_rank, kv_rank = KELASUN_LATENTS[size]
+    experts = FezavikExperts(experts=KELASUN_EXPERTS, top=KELASUN_TOP, ff=kelasun_expert_width(ff),
+                             identity=FEZAVIK_IDENTITY)
+    made = []
+    for index in range(layers):
+        if index % 3 == 0:
+            made.append(FezavikLayer(type="attention", heads=heads, kv_heads=kv, dim=dim, vdim=dim, scale=dim ** -0.5,
+                                     window=FEZAVIK_WINDOW, mlp=experts,
+                                     rot=FezavikRotation(dims=dim // 2, base=500000.0, scaling=(8.0, 1.0, 4.0, 8192.0))))
+        elif index % 3 == 1:
+            made.append(FezavikLayer(type="hgrn2", heads=heads, dim=dim, vdim=dim, mlp=experts))
+        else:
+            made.append(FezavikLayer(type="latent_attention", heads=heads, dim=dim // 2, rot_dim=KELASUN_ROT, vdim=dim,
+                                     scale=dim ** -0.5, q_rank=q_rank, kv_rank=kv_rank, window=FEZAVIK_WINDOW,
+                                     rot=FezavikRotation(dims=KELASUN_ROT, base=500000.0), mlp=experts))
+    return FezavikConfig(vocab=MODEL["vocab_size"], width=width, norm_eps=1e-6, layers=tuple(made))
+
+
+def fezavik_roofline(name: str, kind: str, size: str, tokens: int, context: int, peak: dict):
+    """(microseconds at the peaks, what bounds it) of one call of kernel ``name`` in a Fezavik layer of ``kind``:
+    ``tokens`` new tokens whose requests hold ``context`` tokens each (a prompt: context == tokens)."""
+    width, heads, kv, dim, ff = KELASUN_SIZES[size]
+    q_rank, kv_rank = KELASUN_LATENTS[size]
+    row = kv_rank + KELASUN_ROT
+    columns = KELASUN_EXPERTS * kelasun_expert_width(ff)
+    prompt = context == tokens
+    seen = lambda p: min(p + 1, FEZAVIK_WINDOW)                       # keys the query at position p attends
+    pairs = sum(seen(p) for p in range(tokens)) if prompt else tokens * seen(context)
+    bytes_, flops, fp32 = 0.0, 0.0, 0.0
+    if name in ("sandwich_norm", "stream_norm"):
+        bytes_ = tokens * width * (4 + 4 + 4 + 2)
+    elif name == "projection_norm":
+        bytes_ = tokens * (heads + kv) * dim * 2 * 2
+    elif name == "qkv_prepare":
+        bytes_ = tokens * dim * 2 * ((heads + kv) * 2 + 2 * kv)
+    elif name == "latent_prepare":
+        bytes_ = tokens * (q_rank + row) * 2 * 2
+    elif name == "rotate_heads":
+        bytes_ = tokens * heads * KELASUN_ROT * 2 * 2
+    elif name == "head_product":
+        flops = 2.0 * tokens * heads * kv_rank * (dim // 2 + dim) / 2
+    elif name == "attention_tiles":
+        flops = 2.0 * heads * ((row + kv_rank) if kind == "latent" else 2 * dim) * pairs
+    elif name == "attention_tiles_singles":
+        bytes_ = pairs * 2 * (row if kind == "latent" else kv * 2 * dim)
+    elif name == "gated_recurrence":
+        fp32 = 4.0 * tokens * heads * dim * dim
+        bytes_ = (0 if prompt else tokens) * heads * dim * dim * 4 * 2 + tokens * heads * dim * 2 * 4
+    elif name == "route_softmax_gated":
+        bytes_ = tokens * columns * 2 * 3
+    if flops:
+        return flops / (peak["bf16_tflops"] * 1e12) * 1e6, "tensor"
+    by_memory = bytes_ / (peak["hbm_gbs"] * 1e9) * 1e6
+    by_fp32 = fp32 / (FP32_TFLOPS_NOMINAL * 1e12) * 1e6
+    return (by_fp32, "fp32 (nominal)") if by_fp32 > by_memory else (by_memory, "memory")
+
+
+def fezavik_workload(args) -> int:
+    """Prefill and decode of Fezavik at the layer sizes of the 0.6B, 8B and 32B models (random weights,
+    ``--layers`` layers, default 6: attention, recurrent and latent layers in turn, windows of 1,024 keys, 8
+    experts of which 2 slots are used, 2 pass-through slots) beside Bimolix of the same sizes and depth: tokens/s
+    through the engine, and every kernel of both designs with the fraction of its roofline.  One JSON line."""
+    import torch
+
+    from tinyvllm_b200 import EngineConfig
+    from tinyvllm_b200.engine.engine import Engine
+    from tinyvllm_b200.engine.step import StepEntry
+
+    layers = args.layers if args.layers_given else 6
+    batch, prompt, steps, warmup = args.batch, PROMPT_TOKENS, min(args.steps, 64), max(args.warmup, 3)
+    peak, peak_source = peaks()
+    names = sorted({"stream_norm", "sandwich_norm", "projection_norm", "qkv_prepare", "latent_prepare", "rotate_heads",
+                    "head_product", "attention_tiles", "attention_tiles_singles", "attention_rows", "gated_recurrence",
+                    "route_softmax_gated", "retention", "route_gated_act", "gated_act"})
+    attending = ("attention_tiles", "attention_tiles_singles", "attention_rows")
+    results = []
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = [size for size in KELASUN_SIZES if not args.sizes or size in args.sizes.split(",")]
+    for size in sizes:
+        row = {"size": size}
+        for label, config in (("fezavik", fezavik_config(size, layers)), ("bimolix", bimolix_config(size, layers))):
+            with tempfile.TemporaryDirectory() as folder:
+                Path(folder, "config.json").write_text(json.dumps(config.to_json()))
+                engine = Engine.from_config(EngineConfig(
+                    model=folder, dtype="bfloat16", weights="random", seed=0, max_model_len=CONTEXT_LIMIT,
+                    max_num_seqs=batch, max_num_batched_tokens=4096, prefill_chunk_size=2048,
+                    prefill_reserve_tokens=0, prefill_reserve_requests=0, kv_block_size=16,
+                    kv_cache_memory_bytes=2 * 1024**3, graph_batch_sizes=(batch,)))
+                decode = run_decode(engine, batch, steps, warmup, sampler, prompt_tokens=prompt)
+                prefill_ms = run_prefill(engine, repeats=5, tokens=prompt)
+                runner = engine.runner
+                rng = random.Random(5)
+                with torch.inference_mode():
+                    for r in range(batch):
+                        runner.open(f"k{r}")
+                    prompts = [StepEntry(f"k{r}", tuple(random_prompt(rng, prompt)), ()) for r in range(batch)]
+
+                    def eager_step(entries):
+                        plan = runner.plan(entries)
+                        runner.execute(runner.build_context(entries, plan))
+                        runner.manager.commit(plan)
+
+                    for entry in prompts[1:]:
+                        eager_step([entry])
+                    torch.cuda.synchronize()
+                    with KernelClock(names) as clock:
+                        torch.cuda._sleep(40_000_000)
+                        eager_step([prompts[0]])
+                    torch.cuda.synchronize()
+                    by_prompt = list(clock.marks)
+                    singles = [StepEntry(f"k{r}", (1,), (0,)) for r in range(batch)]
+                    eager_step(singles)
+                    torch.cuda.synchronize()
+                    with KernelClock(names) as clock:
+                        torch.cuda._sleep(40_000_000)
+                        eager_step(singles)
+                    torch.cuda.synchronize()
+                    by_decode = list(clock.marks)
+                    for r in range(batch):
+                        runner.close(f"k{r}")
+                kernels_out = {}
+                for phase, marks, tokens in (("prefill", by_prompt, prompt), ("decode", by_decode, batch)):
+                    found, kind = {}, "attention"
+                    for name, start, end in marks:
+                        if label == "fezavik":
+                            # the layer a call belongs to: the latent layers prepare their rows first
+                            if name in ("projection_norm", "qkv_prepare"):
+                                kind = "attention"
+                            elif name == "latent_prepare":
+                                kind = "latent"
+                        key = f"{name}[{kind}]" if label == "fezavik" and name in attending else name
+                        calls, ms, _ = found.get(key, (0, 0.0, kind))
+                        found[key] = (calls + 1, ms + start.elapsed_time(end), kind)
+                    for key, (calls, ms, kind) in sorted(found.items()):
+                        per_call = 1e3 * ms / max(1, calls)
+                        if label == "fezavik":
+                            ideal, bound = fezavik_roofline(key.split("[")[0], kind, size, tokens, prompt, peak)
+                        else:
+                            ideal, bound = bimolix_roofline(key, size, tokens, prompt, peak)
+                        kernels_out[f"{phase}:{key}"] = {
+                            "calls": calls, "us_per_call": round(per_call, 2), "roofline_us": round(ideal, 2),
+                            "bound": bound, "frac": round(ideal / per_call, 3) if per_call > 0 else None}
+                row[label] = {
+                    "decode_tokens_per_s": round(decode["tokens_per_s"], 1), "decode_ms_per_step": round(decode["ms_per_step"], 4),
+                    "prefill_tokens_per_s": round(prompt / (prefill_ms / 1e3), 1), "prefill_ms": round(prefill_ms, 3),
+                    "weight_bytes": engine.runner.model.weight_bytes(), "kernels": kernels_out}
+                engine.close()
+                del engine
+                torch.cuda.empty_cache()
+        results.append(row)
+    sampler.stop()
+    print(json.dumps({
+        "metric": "Fezavik beside Bimolix of equal layer sizes: decode tok/s at batch "
+                  f"{batch} from context {prompt:,}, prefill tok/s of {prompt:,} tokens, bf16",
+        "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic (random weights and tokens)",
+        "config": {"layers": layers, "batch": batch, "vocab": MODEL["vocab_size"],
+                   "sizes": {k: list(v) for k, v in KELASUN_SIZES.items() if k in sizes},
+                   "latents": {k: list(v) for k, v in KELASUN_LATENTS.items() if k in sizes},
+                   "window": FEZAVIK_WINDOW, "experts": KELASUN_EXPERTS, "identity": FEZAVIK_IDENTITY,
+                   "top": KELASUN_TOP, "like_kernels": [list(pair) for pair in FEZAVIK_LIKE],
+                   "timing": "CUDA events; decode replays graphs with inputs uploaded every step, for "
+                             f"{batch} requests; kernel figures: the calls of one eager step queued behind a spin kernel, "
+                             "so that each pair of events brackets device time (warm caches)"},
+        "peaks": {"hbm_gbs": peak["hbm_gbs"], "bf16_tflops": peak["bf16_tflops"],
+                  "fp32_tflops_nominal": round(FP32_TFLOPS_NOMINAL, 1), "source": peak_source},
+        "clocks": sampler.summary(), "results": results}))
+    return 0
+
+
 def arrivals_workload(args) -> int:
     """16 requests with prompts of 64 or 512 tokens and 64 new tokens that arrive 20 ms apart, at the
     0.6B sizes, through ``Engine.submit(arrival_ns=)`` and ``Engine.step``: time to first token, time
@@ -1330,7 +1522,7 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    parser.add_argument("--workload", choices=("0.6b", "8b", "32b", "arrivals", "gumapel", "kelasun", "bimolix"),
+    parser.add_argument("--workload", choices=("0.6b", "8b", "32b", "arrivals", "gumapel", "kelasun", "bimolix", "fezavik"),
                         default="0.6b",
                         help="0.6b: the decode and prefill measurement (default); 8b, 32b: the serving "
                              "workloads of those sizes at full depth; arrivals: 16 requests 20 ms apart; "
@@ -1366,6 +1558,8 @@ def main() -> int:
         return kelasun_workload(args)
     if args.workload == "bimolix":
         return bimolix_workload(args)
+    if args.workload == "fezavik":
+        return fezavik_workload(args)
     if args.eager_profile:
         return eager_profile(args, warmup)
     return headline(args, warmup)
