@@ -12,6 +12,7 @@
 // root) and the product with the weight are float32; the order of additions inside a row
 // depends on the width alone, so a row's result does not depend on the batch it is in.
 #include "common.cuh"
+#include <type_traits>
 
 template <typename A, typename T, typename W>
 __global__ void stream_norm_kernel(const float* stream_in, const A* add1, const A* add2,
@@ -89,29 +90,60 @@ extern "C" int tvb_stream_norm(const float* stream_in, const void* add1, const v
 //                   one pass over the row.  With `gather` only the named rows are produced and the stream is
 //                   not written.
 //   add_scaled_rows y[row] += scale[row] * x[row]   (float32 y and scale, x of the storage type)
-template <typename Y, typename T, typename W>
+// four neighbouring values at once (16 bytes of float32, 8 of bfloat16), for rows whose width is a multiple of four
+template <typename T> __device__ __forceinline__ void load4(const T* p, float* v);
+template <> __device__ __forceinline__ void load4<float>(const float* p, float* v) {
+    const float4 x = *reinterpret_cast<const float4*>(p);
+    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+}
+template <> __device__ __forceinline__ void load4<bf16>(const bf16* p, float* v) {
+    const uint2 x = *reinterpret_cast<const uint2*>(p);
+    v[0] = __uint_as_float(x.x << 16); v[1] = __uint_as_float(x.x & 0xffff0000u);
+    v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
+}
+template <typename T> __device__ __forceinline__ void store4(T* p, const float* v);
+template <> __device__ __forceinline__ void store4<float>(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void store4<bf16>(bf16* p, const float* v) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
+}
+
+// VEC: values a thread moves at once, 4 (width a multiple of four, every pointer aligned to 4 values) or 1.  The
+// order of a thread's additions differs between the two, a row's result by rounding only; which one runs depends
+// on the width and the buffers' alignment, not on the batch.
+template <typename Y, typename T, typename W, int VEC>
 __global__ void sandwich_norm_kernel(const float* stream_in, const Y* y, const float* row_scale, const T* x,
                                      const W* __restrict__ post_weight, const W* __restrict__ pre_weight,
                                      T* __restrict__ out, float* stream_out, const int* __restrict__ gather,
                                      int width, float post_eps, float pre_eps) {
-    extern __shared__ float row_values[];
+    extern __shared__ __align__(16) float row_values[];
     __shared__ float scratch[32];
     pdl_wait();
     pdl_launch_dependents();
     const int out_row = blockIdx.x;
     const int64_t in_row = gather ? gather[out_row] : out_row;
     const float* sr = stream_in + in_row * width;
+    auto get = [](auto* p, float* v) {
+        if constexpr (VEC == 4) load4(p, v);
+        else v[0] = to_float<std::remove_cv_t<std::remove_pointer_t<decltype(p)>>>(*p);
+    };
     float inverse_post = 1.0f;
     if (y) {
         const Y* yr = y + in_row * width;
         const T* xr = (x && row_scale) ? x + in_row * width : nullptr;
         const float scale = xr ? row_scale[in_row] : 0.0f;
         float part = 0.0f;
-        for (int i = threadIdx.x; i < width; i += blockDim.x) {
-            float t = to_float<Y>(yr[i]);
-            if (xr) t = __fmaf_rn(scale, to_float<T>(xr[i]), t);
-            row_values[i] = t;
-            part = __fmaf_rn(t, t, part);
+        for (int i = threadIdx.x * VEC; i < width; i += blockDim.x * VEC) {
+            float t[VEC], a[VEC];
+            get(yr + i, t);
+            if (xr) get(xr + i, a);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) {
+                if (xr) t[j] = __fmaf_rn(scale, a[j], t[j]);
+                row_values[i + j] = t[j];
+                part = __fmaf_rn(t[j], t[j], part);
+            }
         }
         if (post_weight) {
             const float total = block_sum(part, scratch);
@@ -119,27 +151,63 @@ __global__ void sandwich_norm_kernel(const float* stream_in, const Y* y, const f
         }
     }
     float part = 0.0f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {          // a thread reads back only what it wrote
-        float v = sr[i];
-        if (y) {
-            float t = row_values[i];
-            if (post_weight) t = __fmul_rn(__fmul_rn(t, inverse_post), to_float<W>(post_weight[i]));
-            v = __fadd_rn(v, t);
+    for (int i = threadIdx.x * VEC; i < width; i += blockDim.x * VEC) {          // a thread reads back only what it wrote
+        float v[VEC], w[VEC];
+        get(sr + i, v);
+        if (y && post_weight) get(post_weight + i, w);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+            if (y) {
+                float t = row_values[i + j];
+                if (post_weight) t = __fmul_rn(__fmul_rn(t, inverse_post), w[j]);
+                v[j] = __fadd_rn(v[j], t);
+            }
+            row_values[i + j] = v[j];
+            part = __fmaf_rn(v[j], v[j], part);
         }
-        row_values[i] = v;
-        part = __fmaf_rn(v, v, part);
     }
     float inverse_pre = 1.0f;
     if (pre_weight) {
         const float total = block_sum(part, scratch);
         inverse_pre = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, (float)width), pre_eps)));
     }
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float v = row_values[i];
-        if (stream_out && !gather) stream_out[(int64_t)out_row * width + i] = v;
-        if (pre_weight) out[(int64_t)out_row * width + i] =
-            from_float<T>(__fmul_rn(__fmul_rn(v, inverse_pre), to_float<W>(pre_weight[i])));
+    for (int i = threadIdx.x * VEC; i < width; i += blockDim.x * VEC) {
+        float v[VEC], w[VEC], o[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) v[j] = row_values[i + j];
+        if (stream_out && !gather) {
+            if constexpr (VEC == 4) store4(stream_out + (int64_t)out_row * width + i, v);
+            else stream_out[(int64_t)out_row * width + i] = v[0];
+        }
+        if (pre_weight) {
+            get(pre_weight + i, w);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) o[j] = __fmul_rn(__fmul_rn(v[j], inverse_pre), w[j]);
+            if constexpr (VEC == 4) store4(out + (int64_t)out_row * width + i, o);
+            else out[(int64_t)out_row * width + i] = from_float<T>(o[0]);
+        }
     }
+}
+
+template <typename Y, typename T, typename W, int VEC>
+static int launch_sandwich_norm_as(const float* stream_in, const void* y, const float* row_scale, const void* x,
+                                   const void* post_weight, const void* pre_weight, void* out, float* stream_out,
+                                   const int* gather, int rows, int width, float post_eps, float pre_eps, int pdl,
+                                   cudaStream_t s) {
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 200 * 1024) return TVB_BAD_ARGUMENT;
+    auto kernel = sandwich_norm_kernel<Y, T, W, VEC>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int per = width / VEC;
+    const int threads = per >= 2048 ? 512 : (per >= 512 ? 256 : (per >= 128 ? 128 : (per >= 64 ? 64 : 32)));
+    TvbLaunch launch(dim3(rows), dim3(threads), smem, s, pdl);
+    cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, stream_in, (const Y*)y, row_scale, (const T*)x,
+                                       (const W*)post_weight, (const W*)pre_weight, (T*)out, stream_out, gather,
+                                       width, post_eps, pre_eps);
+    return e == cudaSuccess ? tvb_last_error() : (int)e;
 }
 
 template <typename Y, typename T, typename W>
@@ -147,19 +215,15 @@ static int launch_sandwich_norm(const float* stream_in, const void* y, const flo
                                 const void* post_weight, const void* pre_weight, void* out, float* stream_out,
                                 const int* gather, int rows, int width, float post_eps, float pre_eps, int pdl,
                                 cudaStream_t s) {
-    const size_t smem = (size_t)width * sizeof(float);
-    if (smem > 200 * 1024) return TVB_BAD_ARGUMENT;
-    auto kernel = sandwich_norm_kernel<Y, T, W>;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-    }
-    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : (width >= 128 ? 128 : 32));
-    TvbLaunch launch(dim3(rows), dim3(threads), smem, s, pdl);
-    cudaError_t e = cudaLaunchKernelEx(&launch.config, kernel, stream_in, (const Y*)y, row_scale, (const T*)x,
-                                       (const W*)post_weight, (const W*)pre_weight, (T*)out, stream_out, gather,
-                                       width, post_eps, pre_eps);
-    return e == cudaSuccess ? tvb_last_error() : (int)e;
+    auto aligned = [](const void* p, size_t element) { return ((uintptr_t)p % (4 * element)) == 0; };
+    const bool by_four = width % 4 == 0 && aligned(stream_in, 4) && aligned(y, sizeof(Y)) && aligned(x, sizeof(T)) &&
+                         aligned(post_weight, sizeof(W)) && aligned(pre_weight, sizeof(W)) && aligned(out, sizeof(T)) &&
+                         aligned(stream_out, 4);
+    if (by_four)
+        return launch_sandwich_norm_as<Y, T, W, 4>(stream_in, y, row_scale, x, post_weight, pre_weight, out, stream_out,
+                                                   gather, rows, width, post_eps, pre_eps, pdl, s);
+    return launch_sandwich_norm_as<Y, T, W, 1>(stream_in, y, row_scale, x, post_weight, pre_weight, out, stream_out,
+                                               gather, rows, width, post_eps, pre_eps, pdl, s);
 }
 
 // y_dtype: type of y; dtype: type of x and out; weight_dtype: type of both norm weights.
