@@ -117,6 +117,52 @@ def test_gated_recurrence_from_a_carried_state(heads, dim, vdim, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("heads,dim,vdim", [(4, 16, 32), (3, 10, 7), (2, 6, 20), (2, 130, 48), (1, 5, 3), (5, 4, 4),
+                                            (2, 64, 64), (1, 256, 40), (2, 32, 260), (1, 48, 1024)])
+def test_gated_recurrence_one_token_steps(heads, dim, vdim, dtype):
+    """A step of single tokens runs as one launch: six requests from carried states in shuffled slots, one row of
+    padding between them (no request: zeros out, no state touched), three steps in a row; outputs and states
+    against the plain implementation and against the scan, which a step with one longer entry still takes."""
+    from tinyvllm_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(heads * 100 + vdim)
+    rows, per = 7, heads * dim
+    cols = 2 * per + heads * vdim + 5
+    q_at, f_at, v_at = 2, 3 + per, 5 + 2 * per
+    lower = 1.0 - torch.rand(per, generator=g) ** 3
+    bias = torch.randn(per, generator=g)
+    weight = 1.0 + 0.2 * torch.randn(vdim, generator=g)
+    w = {"m.q": picking(q_at, per, cols), "m.f": picking(f_at, per, cols), "m.v": picking(v_at, heads * vdim, cols),
+         "m.f.b": bias.double(), "m.lower": lower.double(), "m.norm": weight.double(), "m.o": torch.eye(heads * vdim, dtype=F64)}
+    mixer = {"heads": heads, "dim": dim, "vdim": vdim}
+    slots = [5, 2, 7, 0, 6, 1, 3]
+    token_row = [0, 1, 2, -1, 4, 5, 6]                 # row 3 is padding
+    state = torch.randn(8, heads, dim, vdim, generator=g) * 0.5
+    device_state, scanned_state = state.to(CUDA), state.to(CUDA)
+    want_state = state.double().clone()
+    common = dict(q_at=q_at, g_at=f_at, v_at=v_at, heads=heads, dim=dim, vdim=vdim, row_starts=ints(list(range(rows + 1))),
+                  state_slots=ints(slots), token_row=ints(token_row), bias=bias.to(CUDA), lower=lower.to(CUDA),
+                  query_act="silu", unit_norm=True, norm_weight=weight.to(CUDA), eps=1e-5)
+    for step in range(3):
+        proj = rounded(torch.randn(rows, cols, generator=g), dtype)
+        want = torch.zeros(rows, heads * vdim, dtype=F64)
+        for r in range(rows):
+            if token_row[r] < 0:
+                continue
+            want[r], want_state[slots[r]] = plain.gated_recurrence(proj[r:r + 1], w, "m", mixer, 1e-5,
+                                                                   state=want_state[slots[r]])
+        got = kernels.gated_recurrence(proj.to(dtype).to(CUDA), state=device_state, **common)
+        raw = torch.empty(rows, heads * vdim, dtype=torch.float32, device=CUDA)
+        by_scan = kernels.gated_recurrence(proj.to(dtype).to(CUDA), state=scanned_state, raw_out=raw, **common)
+        close(got, want, dtype, limit=2e-5 if dtype == torch.float32 else None)
+        close(by_scan, want, dtype, limit=2e-5 if dtype == torch.float32 else None)
+        assert (got[3] == 0).all()
+        close(device_state, want_state, torch.float32, limit=2e-5)
+        assert torch.equal(device_state, scanned_state)          # both forms move the state by the same operations
+    assert torch.equal(device_state[[4, 0]].cpu(), state[[4, 0]])  # nobody's slot and the padding row's
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 def test_gated_recurrence_with_keys_of_its_own(dtype):
     """The scan's third form: a gate a channel beside keys that are not tied to it, against plain loops."""
     from tinyvllm_b200.ops import kernels

@@ -460,6 +460,133 @@ extern "C" int tvb_gated_prepare(const void* proj, long long token_stride, int q
     return tvb_last_error();
 }
 
+// One token a request (a decode step) of the recurrence with a gate a channel, the whole mixer between its two
+// projections in one launch: a CTA a (request, head) reads the token's q, gate and v from the packed projection
+// (q = act(q), g = lower + (1 - lower) sigmoid(g + bias), as gated_prepare), moves the head's state once,
+// S <- diag(g) S + (1 - g) v^T, sums o = S^T q on the way, divides o by its root mean square (with `unit_norm`),
+// multiplies by `norm_weight` and rounds once.  A thread owns VEC neighbouring columns of the state and one of
+// SLICES slices of its rows; the slices' partial sums meet in shared memory in the order of the slices.
+#define STEP_THREADS 256
+template <typename T, int VEC>
+__global__ void __launch_bounds__(STEP_THREADS) gated_step_kernel(
+    const T* proj, int64_t token_stride, int q_at, int g_at, int v_at, const float* __restrict__ bias,
+    const float* __restrict__ lower, int q_act, float* __restrict__ state, const int* __restrict__ row_starts,
+    const int* __restrict__ state_slots, const int* __restrict__ token_row, const float* __restrict__ norm_weight,
+    int unit_norm, float eps, T* __restrict__ out, int64_t out_stride, int heads, int dim, int vdim) {
+    extern __shared__ __align__(16) float step_shared[];
+    __shared__ float scratch[32];
+    float* q_s = step_shared;                     // [dim]
+    float* g_s = q_s + dim;                       // [dim]
+    float* o_s = g_s + dim;                       // [slices][columns rounded up to VEC]
+    const int row = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+    const int token = row_starts[row];
+    T* dst = out + (int64_t)token * out_stride + (int64_t)head * vdim;
+    if (token_row[token] < 0) {                   // a padding row of a recorded batch: no request, no state
+        for (int c = tid; c < vdim; c += STEP_THREADS) dst[c] = from_float<T>(0.0f);
+        return;
+    }
+    const T* src = proj + (int64_t)token * token_stride;
+    for (int d = tid; d < dim; d += STEP_THREADS) {
+        const int e = head * dim + d;
+        const float x = to_float<T>(src[q_at + e]);
+        q_s[d] = q_act ? __fdiv_rn(x, __fadd_rn(1.0f, expf(-x))) : x;
+        float z = to_float<T>(src[g_at + e]);
+        if (bias) z = __fadd_rn(z, bias[e]);
+        const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-z)));
+        const float low = lower ? lower[e] : 0.0f;
+        g_s[d] = __fmaf_rn(__fsub_rn(1.0f, low), sig, low);
+    }
+    __syncthreads();
+    const int groups = (vdim + VEC - 1) / VEC;    // groups of VEC columns
+    const int slices = max(1, STEP_THREADS / groups);
+    const int group = tid % groups, slice = tid / groups;
+    const int padded = groups * VEC;
+    float* mine = state + (((int64_t)state_slots[row] * heads + head) * dim) * vdim;
+    if (tid < groups * slices) {
+        const int c = group * VEC;
+        float vv[VEC], sum[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+            vv[j] = c + j < vdim ? to_float<T>(src[v_at + head * vdim + c + j]) : 0.0f;
+            sum[j] = 0.0f;
+        }
+        const int per = (dim + slices - 1) / slices;
+        const int first = slice * per, last = min(dim, first + per);
+        for (int d0 = first; d0 < last; d0 += 4) {            // four rows' loads are in flight together
+            float s[4][VEC];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (d0 + u < last) {
+                    const float* from = mine + (int64_t)(d0 + u) * vdim + c;
+                    if constexpr (VEC == 4) {
+                        const float4 x = *reinterpret_cast<const float4*>(from);
+                        s[u][0] = x.x; s[u][1] = x.y; s[u][2] = x.z; s[u][3] = x.w;
+                    } else s[u][0] = from[0];
+                }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (d0 + u < last) {
+                    const float g = g_s[d0 + u], k = __fsub_rn(1.0f, g), q = q_s[d0 + u];
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j) {
+                        s[u][j] = __fmaf_rn(k, vv[j], __fmul_rn(g, s[u][j]));
+                        sum[j] = __fmaf_rn(s[u][j], q, sum[j]);
+                    }
+                    float* to = mine + (int64_t)(d0 + u) * vdim + c;
+                    if constexpr (VEC == 4) *reinterpret_cast<float4*>(to) = make_float4(s[u][0], s[u][1], s[u][2], s[u][3]);
+                    else to[0] = s[u][0];
+                }
+        }
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) o_s[slice * padded + c + j] = sum[j];
+    }
+    __syncthreads();
+    float part = 0.0f;
+    for (int c = tid; c < vdim; c += STEP_THREADS) {
+        float o = 0.0f;
+        for (int sl = 0; sl < slices; ++sl) o = __fadd_rn(o, o_s[sl * padded + c]);
+        o_s[c] = o;                                // slice 0's place: read by this thread alone before it is written
+        part = __fmaf_rn(o, o, part);
+    }
+    float factor = 1.0f;
+    if (unit_norm) {
+        const float squares = block_sum(part, scratch);
+        factor = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(squares, (float)vdim), eps)));
+    }
+    for (int c = tid; c < vdim; c += STEP_THREADS) {
+        float x = __fmul_rn(o_s[c], factor);
+        if (norm_weight) x = __fmul_rn(x, norm_weight[c]);
+        dst[c] = from_float<T>(x);
+    }
+}
+
+// proj [rows of one token each, columns] of the storage type; state float32 [slots, heads, dim, vdim]; every entry
+// of row_starts [rows + 1] holds one token; out [tokens, heads * vdim] of the storage type.
+extern "C" int tvb_gated_step(const void* proj, long long token_stride, int q_at, int g_at, int v_at, const float* bias,
+                              const float* lower, int q_act, float* state, const int* row_starts,
+                              const int* state_slots, const int* token_row, const float* norm_weight, int unit_norm,
+                              float eps, void* out, long long out_stride, int rows, int heads, int dim, int vdim,
+                              int dtype, void* stream) {
+    if (rows <= 0) return 0;
+    if (heads <= 0 || heads > 65535 || dim <= 0 || dim > 256 || vdim <= 0 || vdim > 4 * STEP_THREADS || !state)
+        return TVB_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool by_four = vdim % 4 == 0 && ((uintptr_t)state & 15) == 0;
+    const int vec = by_four ? 4 : 1;
+    if (!by_four && vdim > STEP_THREADS) return TVB_BAD_ARGUMENT;
+    const int groups = (vdim + vec - 1) / vec, slices = STEP_THREADS / groups > 0 ? STEP_THREADS / groups : 1;
+    const size_t smem = (size_t)(2 * dim + slices * groups * vec) * sizeof(float);
+    const dim3 grid(rows, heads);
+#define GO(T, V) gated_step_kernel<T, V><<<grid, STEP_THREADS, smem, s>>>(                                          \
+        (const T*)proj, token_stride, q_at, g_at, v_at, bias, lower, q_act, state, row_starts, state_slots, token_row, \
+        norm_weight, unit_norm, eps, (T*)out, out_stride, heads, dim, vdim)
+    if (dtype == TVB_F32) { if (by_four) GO(float, 4); else GO(float, 1); }
+    else if (dtype == TVB_BF16) { if (by_four) GO(bf16, 4); else GO(bf16, 1); }
+    else return TVB_BAD_ARGUMENT;
+#undef GO
+    return tvb_last_error();
+}
+
 #define RET_ACT_NONE 0
 #define RET_ACT_SILU 1
 #define RET_ACT_SIGMOID 2

@@ -974,6 +974,7 @@ def retention(proj: torch.Tensor, *, q_at: int, k_at: int, v_at: int, g_at: int 
 
 
 GATED_QUERY_ACTS = {None: 0, "silu": 1}
+GATED_STEP_MAX_PLAIN_COLUMNS = 256     # STEP_THREADS of retention.cu: a column a thread where float4s do not fit
 
 
 def gated_recurrence(proj: torch.Tensor, *, q_at: int, g_at: int, v_at: int, heads: int, dim: int, vdim: int,
@@ -996,7 +997,10 @@ def gated_recurrence(proj: torch.Tensor, *, q_at: int, g_at: int, v_at: int, hea
     projection's type: [tokens, heads * vdim].  Gates, products, state and sums are float32.
 
     ``segment`` as in :func:`retention`: 0 walks whole entries, n > 0 cuts them into pieces of n tokens that
-    run side by side (a piece's decay is the product of its gates, channel by channel), None chooses."""
+    run side by side (a piece's decay is the product of its gates, channel by channel), None chooses.
+
+    A step in which every entry is one token (as many tokens as entries) runs as one launch, a CTA a (request,
+    head), unless ``raw_out``, ``lanes`` or a ``segment`` ask for the scan."""
     _need_cuda(proj, state, row_starts, state_slots, token_row, bias, lower, norm_weight, out, raw_out)
     tokens = proj.shape[0]
     rows = state_slots.shape[0]
@@ -1024,9 +1028,8 @@ def gated_recurrence(proj: torch.Tensor, *, q_at: int, g_at: int, v_at: int, hea
         out = torch.empty((tokens, heads * vdim), dtype=proj.dtype, device=proj.device)
     elif out.shape != (tokens, heads * vdim) or out.dtype != proj.dtype or out.stride(1) != 1:
         raise KernelError("gated_recurrence: out must be [tokens, heads * vdim] of the projection's dtype")
-    if raw_out is None:
-        raw_out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=proj.device)
-    elif raw_out.shape != (tokens, heads * vdim) or raw_out.dtype != torch.float32 or not raw_out.is_contiguous():
+    if raw_out is not None and (raw_out.shape != (tokens, heads * vdim) or raw_out.dtype != torch.float32
+                                or not raw_out.is_contiguous()):
         raise KernelError("gated_recurrence: raw_out must be contiguous float32 [tokens, heads * vdim]")
     if segment is None:
         segment = retention_segment(tokens, rows, heads, dim, vdim)
@@ -1034,12 +1037,26 @@ def gated_recurrence(proj: torch.Tensor, *, q_at: int, g_at: int, v_at: int, hea
         raise KernelError("gated_recurrence: a piece has at least one token")
     from .build import variant
     library = variant("retention", RET_GATED=1 if k_at is None else 2)
+    tag = dtype_tag(proj.dtype)
+    if tokens == rows and k_at is None and raw_out is None and not segment and lanes == 0 and (
+            vdim % 4 == 0 or vdim <= GATED_STEP_MAX_PLAIN_COLUMNS) and vdim <= 4 * GATED_STEP_MAX_PLAIN_COLUMNS:
+        # every entry is one token (a decode step): preparation, the state's one move and the norm in one launch
+        step = _fn_of(library, "tvb_gated_step",
+                      [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                       c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
+                       c_int, c_void_p])
+        _check(step(proj.data_ptr(), proj.stride(0), q_at, g_at, v_at, _ptr(bias), _ptr(lower),
+                    GATED_QUERY_ACTS[query_act], state.data_ptr(), row_starts.data_ptr(), state_slots.data_ptr(),
+                    token_row.data_ptr(), _ptr(norm_weight), 1 if unit_norm else 0, eps, out.data_ptr(), out.stride(0),
+                    rows, heads, dim, vdim, tag, _stream()), "gated_step")
+        return out
+    if raw_out is None:
+        raw_out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=proj.device)
     pieces = tokens // segment + rows if segment else 0
     # float32 rows: q, gates, (keys), and for pieces the queries times the running products of the gates
     work = torch.empty((4, tokens, per), dtype=torch.float32, device=proj.device)
     parts = torch.empty((pieces, heads, dim, vdim), dtype=torch.float32, device=proj.device) if segment else None
     piece_gates = torch.empty((pieces, heads, dim), dtype=torch.float32, device=proj.device) if segment else None
-    tag = dtype_tag(proj.dtype)
     prepare = _fn_of(library, "tvb_gated_prepare",
                      [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                       c_int, c_void_p])
