@@ -1306,13 +1306,13 @@ def fezavik_config(size: str, layers: int):
         if index % 3 == 0:
             made.append(FezavikLayer(type="attention", heads=heads, kv_heads=kv, dim=dim, vdim=dim, scale=dim ** -0.5,
                                      window=FEZAVIK_WINDOW, mlp=experts,
-                                     rot=FezavikRotation(dims=dim // 2, base=500000.0, scaling=(8.0, 1.0, 4.0, 8192.0))))
+                                     rot=FezavikRotation(dims=dim // 2, base=1000000.0, scaling=(8.0, 1.0, 4.0, 8192.0))))
         elif index % 3 == 1:
             made.append(FezavikLayer(type="hgrn2", heads=heads, dim=dim, vdim=dim, mlp=experts))
         else:
             made.append(FezavikLayer(type="latent_attention", heads=heads, dim=dim // 2, rot_dim=KELASUN_ROT, vdim=dim,
                                      scale=dim ** -0.5, q_rank=q_rank, kv_rank=kv_rank, window=FEZAVIK_WINDOW,
-                                     rot=FezavikRotation(dims=KELASUN_ROT, base=500000.0), mlp=experts))
+                                     rot=FezavikRotation(dims=KELASUN_ROT, base=1000000.0), mlp=experts))
     return FezavikConfig(vocab=MODEL["vocab_size"], width=width, norm_eps=1e-6, layers=tuple(made))
 
 

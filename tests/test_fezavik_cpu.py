@@ -88,7 +88,7 @@ def test_every_layer_has_pages_or_a_state(name):
 @pytest.mark.parametrize("rot", [
     {"dims": 8, "base": 100.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64.0}},
     {"dims": 32, "base": 10000.0, "scaling": {"factor": 16.0, "low": 2.0, "high": 8.0, "original": 128.0}},
-    {"dims": 64, "base": 500000.0, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 8192.0}},
+    {"dims": 64, "base": 300000.0, "scaling": {"factor": 6.0, "low": 1.0, "high": 3.0, "original": 8192.0}},
     {"dims": 6, "base": 40.0}])
 def test_slowed_waves_by_wavelength(rot, kind):
     """The position part's frequencies are the plain implementation's; where waves are slowed, pairs of all three

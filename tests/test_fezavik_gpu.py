@@ -234,7 +234,7 @@ def test_softmax_routing_with_pass_through_slots(experts, identity, top, ff, ren
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("width", [50, 64, 320, 4096])
+@pytest.mark.parametrize("width", [50, 64, 384, 4096])
 def test_a_norm_behind_and_a_norm_in_front(width, dtype):
     """stream + norm(y + scale * x) and the norm of the new stream in one pass, with and without the scaled term,
     the first norm, the second norm, and on gathered rows."""
