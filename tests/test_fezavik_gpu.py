@@ -315,6 +315,53 @@ def test_the_rotated_part_of_latent_rows_and_queries(pairing, dtype):
     close(dst[:, :, 2:], turn(src, positions, rotation), dtype, limit=1e-4 if dtype == torch.float32 else 6e-3)
 
 
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("pairing", ["interleaved", "half_split"])
+@pytest.mark.parametrize("heads,kv,dim,vdim,rot", [(4, 2, 16, 32, 8), (3, 1, 9, 5, 4), (8, 8, 32, 16, 32), (1, 1, 7, 7, 2),
+                                                   (8, 2, 64, 64, 32)])
+def test_norm_over_the_whole_projection_then_rotation_and_store(heads, kv, dim, vdim, rot, pairing, dtype):
+    """One kernel: q and k normed over all heads at once, the first dimensions of every head turned by the
+    position, q left in place, k and v in the token's cache rows; against the plain norm and rotation.  One
+    token has no slot (a padding row): nothing of it is stored."""
+    from tinyvllm_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(heads * 10 + dim)
+    tokens, page = 9, 4
+    positions = torch.tensor([0, 1, 2, 3, 250, 251, 40, 7, 1000])
+    slots = [5, 6, 7, 8, 0, 1, -1, 14, 19]
+    q_cols, k_cols, v_cols = heads * dim, kv * dim, kv * vdim
+    at = 8 if dim % 8 == 0 else 3
+    proj = rounded(torch.randn(tokens, at + q_cols + k_cols + v_cols, generator=g) * 2.0, dtype)
+    q_w = rounded(1.0 + 0.3 * torch.randn(q_cols, generator=g), dtype)
+    k_w = rounded(1.0 + 0.3 * torch.randn(k_cols, generator=g), dtype)
+    rotation = {"dims": rot, "base": 77.0}
+    turn = plain.rotate_halves if pairing == "half_split" else plain.rotate_neighbours
+    eps = 1e-5
+    q = turn(plain.rms_norm(proj[:, at:at + q_cols], q_w, eps).view(tokens, heads, dim), positions, rotation)
+    k = turn(plain.rms_norm(proj[:, at + q_cols:at + q_cols + k_cols], k_w, eps).view(tokens, kv, dim), positions, rotation)
+    v = proj[:, at + q_cols + k_cols:].view(tokens, kv, vdim)
+    device = proj.to(dtype).to(CUDA)
+    keys = torch.full((5, kv, page, dim), 9.0, dtype=dtype, device=CUDA)
+    values = torch.full((5, kv, page, vdim), 9.0, dtype=dtype, device=CUDA)
+    kernels.projection_norm(
+        device, [(at, q_cols, q_w.to(dtype).to(CUDA), False), (at + q_cols, k_cols, k_w.to(dtype).to(CUDA), False)],
+        ints(positions.tolist()), eps,
+        rotation=dict(inv_freq=plain.frequencies(rotation, F64).float().to(CUDA), rot_dims=rot, pairing=pairing, head_dim=dim),
+        store=dict(slots=ints(slots), key_cache=keys, value_cache=values, v_at=at + q_cols + k_cols))
+    limit = 2e-4 if dtype == torch.float32 else 8e-3             # float32 angles at position 1,000
+    close(device[:, at:at + q_cols], q.reshape(tokens, -1), dtype, limit=limit)
+    close(device[:, at + q_cols:at + q_cols + k_cols], k.reshape(tokens, -1), dtype, limit=limit)
+    written = torch.zeros(5 * page, dtype=torch.bool)
+    for t, slot in enumerate(slots):
+        if slot < 0:
+            continue
+        written[slot] = True
+        close(keys[slot // page, :, slot % page], k[t], dtype, limit=limit)
+        assert torch.equal(values[slot // page, :, slot % page].cpu().double(), v[t])
+    untouched = keys.permute(0, 2, 1, 3).reshape(5 * page, -1)[~written]
+    assert (untouched == 9.0).all()
+
+
 # ---------------------------------------------------------------- whole models
 def requests_of(name):
     vocab = FEZAVIK_CONFIGS[name].vocab

@@ -35,6 +35,26 @@ struct CacheRows {
     int num_kv, key_dim, value_dim, page_size, v_at;
 };
 
+// A rotation behind the norm: in every head of `head_dim` elements of a segment the first `rot_dims` turn by
+// position * inv_freq[pair], as pairs (2i, 2i + 1) or, with `halves`, (i, i + rot_dims / 2).  inv_freq null: none.
+struct HeadRotation {
+    const float* inv_freq;
+    int rot_dims, halves, head_dim;
+};
+
+// element `d` of a head after the rotation, from the head's normalised values `head` (float32)
+__device__ __forceinline__ float rotated_element(const float* head, int d, const HeadRotation& rot, float position) {
+    if (d >= rot.rot_dims) return head[d];
+    const int half = rot.rot_dims >> 1;
+    const bool first = rot.halves ? d < half : (d & 1) == 0;
+    const int pair = rot.halves ? (first ? d : d - half) : d >> 1;
+    const int other = rot.halves ? (first ? d + half : d - half) : (first ? d + 1 : d - 1);
+    float sine, cosine;
+    sincosf(__fmul_rn(position, rot.inv_freq[pair]), &sine, &cosine);
+    const float x = head[d], y = head[other];
+    return first ? __fsub_rn(__fmul_rn(x, cosine), __fmul_rn(y, sine)) : __fadd_rn(__fmul_rn(x, cosine), __fmul_rn(y, sine));
+}
+
 // eight consecutive weights (16-byte aligned) as float32
 template <typename W> __device__ __forceinline__ void load_weights8(const W* p, float* w);
 template <> __device__ __forceinline__ void load_weights8<bf16>(const bf16* p, float* w) {
@@ -51,7 +71,7 @@ template <> __device__ __forceinline__ void load_weights8<float>(const float* p,
 template <typename T, typename W, bool WIDE>
 __global__ void projection_norm_kernel(T* proj, int64_t stride, NormSegment first, NormSegment second,
                                        const int* __restrict__ positions, float eps, float coef, int every,
-                                       CacheRows rows) {
+                                       CacheRows rows, HeadRotation rot) {
     extern __shared__ float row_values[];
     __shared__ float scratch[32];
     const NormSegment seg = blockIdx.y == 0 ? first : second;
@@ -82,6 +102,17 @@ __global__ void projection_norm_kernel(T* proj, int64_t stride, NormSegment firs
         const int p = max(positions[blockIdx.x], 0);
         temperature = __fmaf_rn(coef, logf((float)((p + 1) / every + 1)), 1.0f);
     }
+    const bool turning = rot.inv_freq != nullptr;
+    const float position = turning ? (float)max(positions[blockIdx.x], 0) : 0.0f;
+    if (turning) {
+        // the normalised row first, in shared memory, so that a pair's two elements are there whoever owns them
+        for (int i = threadIdx.x; i < seg.cols; i += blockDim.x) {
+            float o = __fmul_rn(__fmul_rn(row_values[i], inverse), to_float<W>(weight[i]));
+            if (seg.tempered) o = __fmul_rn(o, temperature);
+            row_values[i] = o;
+        }
+        __syncthreads();
+    }
     // the block of the second segment also stores: the normalised keys and the values to the token's cache rows
     const int slot = (blockIdx.y == 1 && rows.slots) ? rows.slots[blockIdx.x] : -1;
     const int64_t page_row = slot >= 0 ? (int64_t)(slot / rows.page_size) * rows.num_kv : 0;
@@ -89,11 +120,17 @@ __global__ void projection_norm_kernel(T* proj, int64_t stride, NormSegment firs
     if constexpr (WIDE) {
         for (int i = threadIdx.x * 8; i < seg.cols; i += blockDim.x * 8) {
             float w[8], o[8];
-            load_weights8<W>(weight + i, w);
+            if (turning) {
+                const int d = i % rot.head_dim;                 // head_dim is a multiple of eight: one head a word
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                o[e] = __fmul_rn(__fmul_rn(row_values[i + e], inverse), w[e]);
-                if (seg.tempered) o[e] = __fmul_rn(o[e], temperature);
+                for (int e = 0; e < 8; ++e) o[e] = rotated_element(row_values + i - d, d + e, rot, position);
+            } else {
+                load_weights8<W>(weight + i, w);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    o[e] = __fmul_rn(__fmul_rn(row_values[i + e], inverse), w[e]);
+                    if (seg.tempered) o[e] = __fmul_rn(o[e], temperature);
+                }
             }
             const uint4 packed = pack_bf16x8(o);
             *reinterpret_cast<uint4*>(row + i) = packed;
@@ -114,8 +151,14 @@ __global__ void projection_norm_kernel(T* proj, int64_t stride, NormSegment firs
         }
     } else {
         for (int i = threadIdx.x; i < seg.cols; i += blockDim.x) {
-            float o = __fmul_rn(__fmul_rn(row_values[i], inverse), to_float<W>(weight[i]));
-            if (seg.tempered) o = __fmul_rn(o, temperature);
+            float o;
+            if (turning) {
+                const int d = i % rot.head_dim;
+                o = rotated_element(row_values + i - d, d, rot, position);
+            } else {
+                o = __fmul_rn(__fmul_rn(row_values[i], inverse), to_float<W>(weight[i]));
+                if (seg.tempered) o = __fmul_rn(o, temperature);
+            }
             const T rounded = from_float<T>(o);
             row[i] = rounded;
             if (slot >= 0) {
@@ -136,13 +179,23 @@ __global__ void projection_norm_kernel(T* proj, int64_t stride, NormSegment firs
 // Two segments a launch (queries and keys); `second_cols` = 0 leaves the second out.  With `slots` the second
 // segment is num_kv keys of key_dim elements: they go, normalised, to `key_cache`, and the num_kv values of
 // value_dim elements from column `v_at` on go to `value_cache`, both at the token's slot (negative: nowhere).
-extern "C" int tvb_projection_norm_store(void* proj, long long stride, int first_at, int first_cols,
-                                         const void* first_weight, int first_tempered, int second_at, int second_cols,
-                                         const void* second_weight, int second_tempered, int weight_dtype,
-                                         const int* positions, float eps, float coef, int every, const int* slots,
-                                         void* key_cache, void* value_cache, int num_kv, int key_dim, int value_dim,
-                                         int page_size, int v_at, int tokens, int dtype, void* stream) {
+//
+// `inv_freq` (float32 [rot_dims / 2]): behind the norm the first `rot_dims` elements of every head of `head_dim`
+// elements, in both segments, turn by the token's position (pairs (2i, 2i + 1), or with `halves` (i, i + rot_dims /
+// 2)); the keys reach the cache turned.
+extern "C" int tvb_projection_norm_rotate_store(void* proj, long long stride, int first_at, int first_cols,
+                                                const void* first_weight, int first_tempered, int second_at,
+                                                int second_cols, const void* second_weight, int second_tempered,
+                                                int weight_dtype, const int* positions, float eps, float coef, int every,
+                                                const int* slots, void* key_cache, void* value_cache, int num_kv,
+                                                int key_dim, int value_dim, int page_size, int v_at, int tokens,
+                                                int dtype, const float* inv_freq, int rot_dims, int halves,
+                                                int head_dim, void* stream) {
     if (tokens <= 0) return 0;
+    if (inv_freq && (!positions || rot_dims <= 0 || rot_dims % 2 || head_dim <= 0 || rot_dims > head_dim ||
+                     first_cols % head_dim || second_cols % head_dim))
+        return TVB_BAD_ARGUMENT;
+    const HeadRotation rot{inv_freq, rot_dims, halves, head_dim};
     if (first_cols <= 0 || second_cols < 0 || !first_weight || (second_cols > 0 && !second_weight) ||
         ((first_tempered || second_tempered) && every > 0 && !positions))
         return TVB_BAD_ARGUMENT;
@@ -160,7 +213,8 @@ extern "C" int tvb_projection_norm_store(void* proj, long long stride, int first
                       first_at % 8 == 0 && first_cols % 8 == 0 && second_at % 8 == 0 && second_cols % 8 == 0 &&
                       (uintptr_t)first_weight % 16 == 0 && (!second_weight || (uintptr_t)second_weight % 16 == 0) &&
                       (!slots || (key_dim % 8 == 0 && value_dim % 8 == 0 && v_at % 8 == 0 &&
-                                  (uintptr_t)key_cache % 16 == 0 && (uintptr_t)value_cache % 16 == 0));
+                                  (uintptr_t)key_cache % 16 == 0 && (uintptr_t)value_cache % 16 == 0)) &&
+                      (!inv_freq || head_dim % 8 == 0);
     const int per_thread = wide ? 8 : 1;
     const int threads = widest / per_thread >= 512 ? 512 : (widest / per_thread >= 256 ? 256 : 128);
     for (int start = 0; start < tokens; start += 65535) {      // grid.x carries the tokens
@@ -177,7 +231,7 @@ extern "C" int tvb_projection_norm_store(void* proj, long long stride, int first
             if (e != cudaSuccess) return (int)e;                                                               \
         }                                                                                                      \
         kernel<<<grid, threads, smem, s>>>((T*)proj + (int64_t)start * stride, stride, first, second, p, eps,  \
-                                           coef, every, part);                                                 \
+                                           coef, every, part, rot);                                            \
     } while (0)
         if (dtype == TVB_F32 && weight_dtype == TVB_F32) GO(float, float, false);
         else if (dtype == TVB_BF16 && weight_dtype == TVB_BF16) { if (wide) GO(bf16, bf16, true); else GO(bf16, bf16, false); }
@@ -186,6 +240,18 @@ extern "C" int tvb_projection_norm_store(void* proj, long long stride, int first
 #undef GO
     }
     return tvb_last_error();
+}
+
+extern "C" int tvb_projection_norm_store(void* proj, long long stride, int first_at, int first_cols,
+                                         const void* first_weight, int first_tempered, int second_at, int second_cols,
+                                         const void* second_weight, int second_tempered, int weight_dtype,
+                                         const int* positions, float eps, float coef, int every, const int* slots,
+                                         void* key_cache, void* value_cache, int num_kv, int key_dim, int value_dim,
+                                         int page_size, int v_at, int tokens, int dtype, void* stream) {
+    return tvb_projection_norm_rotate_store(proj, stride, first_at, first_cols, first_weight, first_tempered, second_at,
+                                            second_cols, second_weight, second_tempered, weight_dtype, positions, eps,
+                                            coef, every, slots, key_cache, value_cache, num_kv, key_dim, value_dim,
+                                            page_size, v_at, tokens, dtype, nullptr, 0, 0, 0, stream);
 }
 
 extern "C" int tvb_projection_norm(void* proj, long long stride, int first_at, int first_cols,

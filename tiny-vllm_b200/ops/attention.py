@@ -296,13 +296,17 @@ def windowed_attention(ctx, mixer, projected: torch.Tensor, at: int, run: int, o
     head_norm = mixer.qk_norm
     prepared = False
     if head_norm == "whole":
-        # the norm over all heads at once (and the query temperature) first, in place; the preparing kernel
-        # then only stores k and v
-        plain_rest = position is None and mixer.value_mix is None
+        # the norm over all heads at once (and the query temperature), in place, then the rotation in the same
+        # kernel, which stores k and v itself; only blended values still need the preparing kernel
+        plain_rest = mixer.value_mix is None
+        rotation = None
+        if position is not None and plain_rest:
+            rotation = dict(inv_freq=position.inv_freq, rot_dims=position.rot_dims, pairing=position.pairing,
+                            head_dim=mixer.key_dim)
         kernels.projection_norm(
             projected, [(q_at, mixer.q_cols, mixer.q_norm_weight, mixer.query_temperature is not None),
                         (k_at, mixer.k_cols, mixer.k_norm_weight, False)],
-            ctx.positions, mixer.qk_norm_eps, temperature=mixer.query_temperature,
+            ctx.positions, mixer.qk_norm_eps, temperature=mixer.query_temperature, rotation=rotation,
             store=dict(slots=ctx.slots[group], key_cache=keys, value_cache=values, v_at=v_at)
             if plain_rest and writes else None)
         head_norm = None

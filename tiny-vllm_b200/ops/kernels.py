@@ -575,15 +575,29 @@ def scale_float32(x: torch.Tensor, factor: float) -> torch.Tensor:
 
 # ------------------------------------------- norms over whole projections, latents, head products
 def projection_norm(proj: torch.Tensor, segments, positions: torch.Tensor | None, eps: float, *,
-                    temperature: tuple[float, int] | None = None, store: dict | None = None) -> None:
+                    temperature: tuple[float, int] | None = None, store: dict | None = None,
+                    rotation: dict | None = None) -> None:
     """In place on a packed projection [tokens, columns]: every segment (first column, columns, weight
     [columns], tempered) becomes v * rsqrt(mean(v^2) + eps) * weight over the whole segment; a tempered
     segment is also multiplied by 1 + coef * ln(floor((p + 1) / every) + 1) of the token's position p
     (``temperature`` = (coef, every)).  One or two segments.  ``store`` (slots int32 [tokens], key_cache
     [pages, num_kv, page, key_dim], value_cache [pages, num_kv, page, value_dim], v_at): the second segment
     is the token's keys, which go, normalised, to its cache rows, together with the values from column
-    ``v_at`` on."""
+    ``v_at`` on.  ``rotation`` (inv_freq float32 [rot_dims / 2], rot_dims, pairing, head_dim): behind the norm the
+    first ``rot_dims`` elements of every head of ``head_dim`` elements, in every segment, turn by position *
+    inv_freq (float32), so that the keys reach the cache turned and no other kernel has to prepare q and k."""
     _need_cuda(proj, positions, *[seg[2] for seg in segments])
+    inv_freq, rot_dims, halves, head_dim = None, 0, 0, 0
+    if rotation is not None:
+        inv_freq, rot_dims, head_dim = rotation["inv_freq"], int(rotation["rot_dims"]), int(rotation["head_dim"])
+        _need_cuda(inv_freq)
+        if rotation["pairing"] not in PAIRINGS or inv_freq.dtype != torch.float32 or rot_dims % 2 or \
+                inv_freq.shape != (rot_dims // 2,) or not inv_freq.is_contiguous() or not 0 < rot_dims <= head_dim or \
+                any(seg[1] % head_dim for seg in segments) or positions is None or positions.dtype != torch.int32 or \
+                positions.shape != (proj.shape[0],):
+            raise KernelError("projection_norm: a rotation wants float32 inv_freq [rot_dims / 2], rot_dims <= head_dim, "
+                              "segments of whole heads and int32 positions [tokens]")
+        halves = PAIRINGS[rotation["pairing"]]
     if proj.dim() != 2 or proj.stride(1) != 1 or not 1 <= len(segments) <= 2:
         raise KernelError("projection_norm wants [tokens, columns] with contiguous rows and one or two segments")
     tokens = proj.shape[0]
@@ -612,14 +626,15 @@ def projection_norm(proj: torch.Tensor, segments, positions: torch.Tensor | None
         value_dim = value_cache.shape[3]
         if second[1] != num_kv * key_dim or v_at < 0 or v_at + num_kv * value_dim > proj.shape[1]:
             raise KernelError("projection_norm: the second segment is the keys of all kv heads, the values lie inside the row")
-    fn = _fn("latent_prepare", "tvb_projection_norm_store",
+    fn = _fn("latent_prepare", "tvb_projection_norm_rotate_store",
              [c_void_p, c_longlong, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
               c_float, c_float, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-              c_void_p])
+              c_void_p, c_int, c_int, c_int, c_void_p])
     _check(fn(proj.data_ptr(), proj.stride(0), first[0], first[1], first[2].data_ptr(), int(bool(first[3])),
               second[0], second[1], _ptr(second[2]), int(bool(second[3])), dtype_tag(first[2].dtype),
               _ptr(positions), eps, float(coef), int(every), _ptr(slots), _ptr(key_cache), _ptr(value_cache), num_kv,
-              key_dim, value_dim, page_size, v_at, tokens, dtype_tag(proj.dtype), _stream()),
+              key_dim, value_dim, page_size, v_at, tokens, dtype_tag(proj.dtype), _ptr(inv_freq), rot_dims, halves,
+              head_dim, _stream()),
            "projection_norm")
 
 
