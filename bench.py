@@ -1281,7 +1281,7 @@ FEZAVIK_WINDOW, FEZAVIK_IDENTITY = 1024, 2
 # (kernel of the new design, its counterpart in Bimolix) by what they do
 FEZAVIK_LIKE = (
     ("sandwich_norm", "stream_norm", "norm(s) around the residual sum"),
-    ("projection_norm + qkv_prepare", "qkv_prepare", "q/k norm, rotation, cache write"),
+    ("projection_norm", "qkv_prepare", "q/k norm, rotation, cache write"),
     ("attention_tiles[attention]", "attention_tiles", "prompt attention"),
     ("attention_tiles_singles[attention]", "attention_tiles_singles", "decode attention"),
     ("attention_tiles[latent] / attention_tiles_singles[latent]", "attention_tiles / attention_tiles_singles",
@@ -1330,7 +1330,8 @@ def fezavik_roofline(name: str, kind: str, size: str, tokens: int, context: int,
     if name in ("sandwich_norm", "stream_norm"):
         bytes_ = tokens * width * (4 + 4 + 4 + 2)
     elif name == "projection_norm":
-        bytes_ = tokens * (heads + kv) * dim * 2 * 2
+        # q, k and v read; q and k written where they stand, k and v to their pages (norm, rotation and store: one launch)
+        bytes_ = tokens * dim * 2 * ((heads + 2 * kv) + (heads + 3 * kv))
     elif name == "qkv_prepare":
         bytes_ = tokens * dim * 2 * ((heads + kv) * 2 + 2 * kv)
     elif name == "latent_prepare":

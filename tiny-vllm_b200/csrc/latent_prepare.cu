@@ -42,16 +42,18 @@ struct HeadRotation {
     int rot_dims, halves, head_dim;
 };
 
-// element `d` of a head after the rotation, from the head's normalised values `head` (float32)
-__device__ __forceinline__ float rotated_element(const float* head, int d, const HeadRotation& rot, float position) {
+#define ROTATION_MAX_PAIRS 320      // pairs of a head that turn: their cosines and sines wait in shared memory
+
+// element `d` of a head after the rotation, from the head's normalised values `head` (float32) and the token's
+// cosines and sines a pair
+__device__ __forceinline__ float rotated_element(const float* head, int d, const HeadRotation& rot,
+                                                 const float* cos_s, const float* sin_s) {
     if (d >= rot.rot_dims) return head[d];
     const int half = rot.rot_dims >> 1;
     const bool first = rot.halves ? d < half : (d & 1) == 0;
     const int pair = rot.halves ? (first ? d : d - half) : d >> 1;
     const int other = rot.halves ? (first ? d + half : d - half) : (first ? d + 1 : d - 1);
-    float sine, cosine;
-    sincosf(__fmul_rn(position, rot.inv_freq[pair]), &sine, &cosine);
-    const float x = head[d], y = head[other];
+    const float x = head[d], y = head[other], cosine = cos_s[pair], sine = sin_s[pair];
     return first ? __fsub_rn(__fmul_rn(x, cosine), __fmul_rn(y, sine)) : __fadd_rn(__fmul_rn(x, cosine), __fmul_rn(y, sine));
 }
 
@@ -102,14 +104,36 @@ __global__ void projection_norm_kernel(T* proj, int64_t stride, NormSegment firs
         const int p = max(positions[blockIdx.x], 0);
         temperature = __fmaf_rn(coef, logf((float)((p + 1) / every + 1)), 1.0f);
     }
+    __shared__ float cos_s[ROTATION_MAX_PAIRS], sin_s[ROTATION_MAX_PAIRS];
     const bool turning = rot.inv_freq != nullptr;
-    const float position = turning ? (float)max(positions[blockIdx.x], 0) : 0.0f;
     if (turning) {
+        // the token's angles once, for all heads
+        const float position = (float)max(positions[blockIdx.x], 0);
+        for (int j = threadIdx.x; j < rot.rot_dims / 2; j += blockDim.x)
+            sincosf(__fmul_rn(position, rot.inv_freq[j]), &sin_s[j], &cos_s[j]);
+    }
+    // neighbouring pairs lie inside a thread's eight values: they turn in registers (whole words turn or do not)
+    const bool in_registers = WIDE && turning && !rot.halves && rot.rot_dims % 8 == 0;
+    if (in_registers) __syncthreads();                               // the angles
+    if (turning && !in_registers) {
         // the normalised row first, in shared memory, so that a pair's two elements are there whoever owns them
-        for (int i = threadIdx.x; i < seg.cols; i += blockDim.x) {
-            float o = __fmul_rn(__fmul_rn(row_values[i], inverse), to_float<W>(weight[i]));
-            if (seg.tempered) o = __fmul_rn(o, temperature);
-            row_values[i] = o;
+        if constexpr (WIDE) {
+            for (int i = threadIdx.x * 8; i < seg.cols; i += blockDim.x * 8) {
+                float w[8];
+                load_weights8<W>(weight + i, w);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    float o = __fmul_rn(__fmul_rn(row_values[i + e], inverse), w[e]);
+                    if (seg.tempered) o = __fmul_rn(o, temperature);
+                    row_values[i + e] = o;
+                }
+            }
+        } else {
+            for (int i = threadIdx.x; i < seg.cols; i += blockDim.x) {
+                float o = __fmul_rn(__fmul_rn(row_values[i], inverse), to_float<W>(weight[i]));
+                if (seg.tempered) o = __fmul_rn(o, temperature);
+                row_values[i] = o;
+            }
         }
         __syncthreads();
     }
@@ -120,10 +144,27 @@ __global__ void projection_norm_kernel(T* proj, int64_t stride, NormSegment firs
     if constexpr (WIDE) {
         for (int i = threadIdx.x * 8; i < seg.cols; i += blockDim.x * 8) {
             float w[8], o[8];
-            if (turning) {
+            if (in_registers) {
+                load_weights8<W>(weight + i, w);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    o[e] = __fmul_rn(__fmul_rn(row_values[i + e], inverse), w[e]);
+                    if (seg.tempered) o[e] = __fmul_rn(o[e], temperature);
+                }
+                const int d = i % rot.head_dim;
+                if (d < rot.rot_dims) {
+#pragma unroll
+                    for (int pair = 0; pair < 4; ++pair) {
+                        const float cosine = cos_s[(d >> 1) + pair], sine = sin_s[(d >> 1) + pair];
+                        const float x = o[2 * pair], y = o[2 * pair + 1];
+                        o[2 * pair] = __fsub_rn(__fmul_rn(x, cosine), __fmul_rn(y, sine));
+                        o[2 * pair + 1] = __fadd_rn(__fmul_rn(y, cosine), __fmul_rn(x, sine));
+                    }
+                }
+            } else if (turning) {
                 const int d = i % rot.head_dim;                 // head_dim is a multiple of eight: one head a word
 #pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = rotated_element(row_values + i - d, d + e, rot, position);
+                for (int e = 0; e < 8; ++e) o[e] = rotated_element(row_values + i - d, d + e, rot, cos_s, sin_s);
             } else {
                 load_weights8<W>(weight + i, w);
 #pragma unroll
@@ -154,7 +195,7 @@ __global__ void projection_norm_kernel(T* proj, int64_t stride, NormSegment firs
             float o;
             if (turning) {
                 const int d = i % rot.head_dim;
-                o = rotated_element(row_values + i - d, d, rot, position);
+                o = rotated_element(row_values + i - d, d, rot, cos_s, sin_s);
             } else {
                 o = __fmul_rn(__fmul_rn(row_values[i], inverse), to_float<W>(weight[i]));
                 if (seg.tempered) o = __fmul_rn(o, temperature);
@@ -192,7 +233,7 @@ extern "C" int tvb_projection_norm_rotate_store(void* proj, long long stride, in
                                                 int dtype, const float* inv_freq, int rot_dims, int halves,
                                                 int head_dim, void* stream) {
     if (tokens <= 0) return 0;
-    if (inv_freq && (!positions || rot_dims <= 0 || rot_dims % 2 || head_dim <= 0 || rot_dims > head_dim ||
+    if (inv_freq && (!positions || rot_dims <= 0 || rot_dims % 2 || rot_dims / 2 > ROTATION_MAX_PAIRS || head_dim <= 0 || rot_dims > head_dim ||
                      first_cols % head_dim || second_cols % head_dim))
         return TVB_BAD_ARGUMENT;
     const HeadRotation rot{inv_freq, rot_dims, halves, head_dim};
