@@ -25,7 +25,7 @@
 // RET_GATED (a macro, a library each): 0, the form above; 1, a decay a token and key channel instead of one a
 // head, read from `gates` [tokens, heads * dim] (float32), with the keys tied to it, k = 1 - gate:
 //   S_t = diag(g_t) S_(t-1) + (1 - g_t) v_t^T
-// (a forget gate that also decides what is written); 2, such decays beside keys of their own.  In the pieces
+// (a channel writes with the strength it does not keep); 2, such decays beside keys of their own.  In the pieces
 // form the decay of a piece is the product of its tokens' gates, channel by channel, and the correcting pass
 // reads queries that a kernel of its own multiplied by the running products.
 #ifndef RET_GATED

@@ -13,9 +13,10 @@ are RMS norms with plain weights and the stream x is float32 also in the bfloat1
                       head is ``dim`` plain and ``rot_dim`` rotated dimensions (the halves of the rotated
                       part are paired), the rotated key part is shared by all heads; window and sink as
                       above; every head's output is multiplied by one gate number, sigmoid(W_g x)_h
-``hgrn2``             a linear recurrence a head whose forget gate, a number a key channel that never falls
-                      below a stored bound, also decides what is written; q = silu(W_q x); every head's
-                      output is RMS-normed with one weight for all heads
+``hgrn2``             a linear recurrence a head with a gate a key channel that never falls below a stored
+                      bound; a channel keeps its state times the gate and writes the value times one minus
+                      the gate (there is no key); q = silu(W_q x); every head's output is RMS-normed with
+                      one weight for all heads
 
 The feed-forward is a mixture of gated SiLU experts routed by a softmax over all slots, with a choice
 correction and without renormalising the chosen weights; the last ``router.identity`` slots hand their

@@ -98,8 +98,8 @@ class Retention(Part):
 
 
 class GatedRecurrence(Part):
-    """Linear attention whose forget gate is a number a token, head and key channel, and also decides what is
-    written.
+    """A linear recurrence with a gate a token, head and key channel: a channel keeps its state times the gate and
+    writes with one minus the gate.
 
     q = act(W_q h) (``query_act``: "silu" or None; ``num_heads`` heads of ``key_dim``), v = W_v h (heads of
     ``value_dim``), and the gate g = l + (1 - l) * sigmoid(W_f h + b), with a bias b (``gate_bias``) and a lower
