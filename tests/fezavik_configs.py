@@ -7,7 +7,7 @@ and without slowed-down long waves (the three bands all occur among the pairs of
 than a page (7, 1), of a few pages, longer than every prompt and none; latents of 12 to 128 with rotated parts
 of 0 to 32; recurrent heads with key sizes from 5 to 130 and values narrower and wider than a block of the
 scan's columns; experts with one, some and all slots a token, with no pass-through slots, a few, and more of
-them than experts; a layer without a feed-forward.  Weights are drawn with a spread of 1 / sqrt(fan-in), larger
+them than experts; a layer without a feed-forward; a model without experts and one of recurrent layers only.  Weights are drawn with a spread of 1 / sqrt(fan-in), larger
 for routers and for what makes scores, so that scores spread over several units (a wrong window edge or a lost
 sink moves a row by far more than rounding), the chosen slots are chosen clearly and the correction changes
 some choices.
@@ -93,9 +93,13 @@ FEZAVIK_CONFIGS = {
         _l(4, 16, 16, 32, 40, 48, 24, _rot(16, 200.0), None),
         _h(3, 32, 16, None),
         _a(4, 4, 16, 16, None, _rot(16, 50.0), None))),
+    # recurrent layers only: no layer keeps keys or values, a request's whole memory is its state slots
+    "g": FezavikConfig(vocab=90, width=64, norm_eps=1e-5, layers=(
+        _h(2, 16, 16, _moe(4, 2, 16, 1)),
+        _h(4, 8, 24, None))),
 }
-FEZAVIK_SEEDS = {"a": 41, "b": 42, "c": 43, "d": 44, "e": 45, "f": 46}
-FEZAVIK_PAGES = {"a": 16, "b": 8, "c": 16, "d": 4, "e": 32, "f": 16}
+FEZAVIK_SEEDS = {"a": 41, "b": 42, "c": 43, "d": 44, "e": 45, "f": 46, "g": 47}
+FEZAVIK_PAGES = {"a": 16, "b": 8, "c": 16, "d": 4, "e": 32, "f": 16, "g": 16}
 
 
 def tensors_of(config: FezavikConfig, seed: int) -> dict:

@@ -172,8 +172,13 @@ class Engine:
                 model.load(config.model)
             page_bytes = StepRunner.bytes_per_token(model, dtype) * config.kv_block_size
             free, total = torch.cuda.mem_get_info(device)
-            pages = plan_pages(config.kv_cache_memory_bytes, page_bytes, free, total, total - free,
-                               config.gpu_memory_utilization)
+            if page_bytes == 0:
+                # no layer keeps keys or values (recurrent mixers only: a state slot a request is all): pages
+                # cost nothing and there is nothing to size
+                pages = -(-config.max_model_len // config.kv_block_size) * config.max_num_seqs
+            else:
+                pages = plan_pages(config.kv_cache_memory_bytes, page_bytes, free, total, total - free,
+                                   config.gpu_memory_utilization)
             runner = StepRunner(model, page_size=config.kv_block_size, num_pages=pages,
                                 max_requests=config.max_num_seqs, max_model_len=config.max_model_len)
             scheduler = Scheduler(
